@@ -121,6 +121,13 @@ OA_API const char* oa_http_last_error(void);
 /* ---- measurement + parity hooks (used by bench.py and tests/; not part of the Go seam) ---- */
 /* fresh single-sequence prefill of `tokens`; fp32 logits of every position -> logits_out[n, vocab] */
 OA_API int oa_debug_prefill_logits(oa_engine*, const int32_t* tokens, int32_t n, float* logits_out);
+/* Step-by-step replay of given token ids (bin/trace_run): entry e brings the next n_tokens[e] tokens of request ids[e] (a whole prompt, a
+ * portion of one, or a single token; a request is admitted at its first entry) and n_want[e] places among them whose logits are wanted.
+ * `tokens` and `want` are the entries' lists back to back.  All entries of a call are ONE batch through the engine's own forward, cache
+ * pages and state slots; nothing is sampled.  logits_out (host, fp32 [sum n_want, vocab], at least logits_cap_rows rows) is filled in entry
+ * order.  Requests listed in end_ids return their pages and state slot after the step. */
+OA_API int oa_trace_step(oa_engine*, int32_t n_entries, const int64_t* ids, const int32_t* n_tokens, const int32_t* tokens, const int32_t* n_want,
+                         const int32_t* want, int32_t n_end, const int64_t* end_ids, float* logits_out, int64_t logits_cap_rows);
 /* Device-resident decode benchmark: builds `batch` sequences of `ctx_len` cached tokens (real chunked prefill of
  * seeded synthetic ids), then runs warmup+steps decode forwards of the whole batch, timed with CUDA events on the
  * engine stream.  out[0]=ms/step over ONE event bracket around all timed steps (host gaps included), out[1]=prefill ms, out[2]=kernel launches per step, out[3]=mean ctx over the

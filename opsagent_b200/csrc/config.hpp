@@ -4,10 +4,13 @@
 #include <cstdint>
 #include <cstdlib>
 #include <map>
+#include <memory>
 #include <sstream>
 #include <stdexcept>
 #include <string>
 #include <vector>
+
+#include "hybrid_config.hpp"
 
 namespace oa {
 
@@ -66,6 +69,10 @@ struct ModelConfig {
     float init_std = 0.02f;
     uint64_t seed = 1234;
     std::string chat_template = "llama3";   // or "chatml"
+    // model registry key: "llama" (Llama-3 / Qwen2.5 decoders, the fields above) or "ratasun" (the hybrid family; sizes in `hybrid`, read from
+    // the checkpoint folder's config.json, whose "architecture" key selects the class)
+    std::string arch = "llama";
+    std::shared_ptr<HybridConfig> hybrid;
 
     int q_dim() const { return n_heads * head_dim; }
     int kv_dim() const { return n_kv_heads * head_dim; }
@@ -108,6 +115,9 @@ struct EngineOptions {
     int sk_l2_prefetch_kb = 0;    // per-CTA weight KB prefetched into L2 ahead of the dependency wait (measured: hurts, 8.75 -> 9.3 ms; off)
     int sk_bn_qkv = 0, sk_bn_o = 0, sk_bn_gu = 0, sk_bn_down = 0;   // per-projection overrides (0 = sk_bn)
     int start_thread = 1;
+    std::string model_dir;        // checkpoint folder (config.json + model.safetensors): the model class is chosen by config.json's "architecture"
+    int f32 = 0;                  // "dtype": "float32" — everything in fp32 (hybrid family only); default bf16 matrices and activations with fp32 accumulation
+    int hy_tensor_core = 1;       // hybrid family, bf16: projections and grouped expert products on the tcgen05 GEMM (0: the plain FMA kernels everywhere)
     std::string model_aliases;    // other model names this engine answers to, comma separated ("*" = any): the reference sends currentModel or "gpt-4" (execute.go:168-171)
     std::string weights;          // path of a Hugging Face *.safetensors file or shard directory (empty: seeded random init)
     int prefix_cache = 1;         // reuse KV pages of shared prompt prefixes across requests (the ReAct loop resends its history)
@@ -130,7 +140,17 @@ struct EngineOptions {
 inline void parse_config(const std::string& json, ModelConfig& m, EngineOptions& o) {
     JsonFlat j = JsonFlat::parse(json);
     std::string name = j.s("model", "custom");
-    if (!preset_model(name, m)) m.name = name;
+    o.model_dir = j.s("model_dir", o.model_dir);
+    const std::string dtype = j.s("dtype", "bfloat16");
+    if (dtype != "bfloat16" && dtype != "float32") throw std::runtime_error("dtype must be bfloat16 or float32");
+    o.f32 = dtype == "float32";
+    if (!o.model_dir.empty()) {
+        const std::string arch = HybridConfig::architecture_of(o.model_dir);
+        if (arch != "Ratasun") throw std::runtime_error("unknown model architecture '" + arch + "' in " + o.model_dir + "/config.json");
+        m.arch = "ratasun"; m.hybrid = std::make_shared<HybridConfig>(HybridConfig::load(o.model_dir));
+        m.name = name == "custom" ? "ratasun" : name;
+        m.hidden = m.hybrid->width; m.vocab = m.hybrid->vocab; m.n_layers = (int)m.hybrid->runs.size(); m.rms_eps = m.hybrid->eps;
+    } else if (!preset_model(name, m)) m.name = name;
     auto I = [&](const char* k, int& v) { v = (int)j.i(k, v); };
     auto F = [&](const char* k, float& v) { v = (float)j.f(k, v); };
     I("hidden", m.hidden); I("n_layers", m.n_layers); I("n_heads", m.n_heads); I("n_kv_heads", m.n_kv_heads);
@@ -145,6 +165,11 @@ inline void parse_config(const std::string& json, ModelConfig& m, EngineOptions&
     I("max_seq_len", o.max_seq_len); I("max_step_tokens", o.max_step_tokens); I("max_queue", o.max_queue);
     I("bn_qkv", o.bn_qkv); I("bn_o", o.bn_o); I("bn_gu", o.bn_gu); I("bn_down", o.bn_down); I("bn_lm", o.bn_lm);
     I("attn_ctas", o.attn_ctas); I("streamk", o.streamk); I("sk_bn", o.sk_bn); I("sk_ctas", o.sk_ctas); I("sk_l2_prefetch_kb", o.sk_l2_prefetch_kb); I("sk_max_rows", o.sk_max_rows); I("sk_fuse_swiglu", o.sk_fuse_swiglu); I("sk_fuse_epi", o.sk_fuse_epi); I("sk_clusterk", o.sk_clusterk); I("sk_clusterk_min_fill", o.sk_clusterk_min_fill); I("sk_bn_qkv", o.sk_bn_qkv); I("sk_bn_o", o.sk_bn_o); I("sk_bn_gu", o.sk_bn_gu); I("sk_bn_down", o.sk_bn_down); I("start_thread", o.start_thread); o.weights = j.s("weights", o.weights); o.model_aliases = j.s("model_aliases", o.model_aliases); o.tokenizer = j.s("tokenizer", o.tokenizer); I("prefix_cache", o.prefix_cache); I("json_mode", o.json_mode); I("react_tool_steps", o.react_tool_steps); I("prefill_batch_tokens", o.prefill_batch_tokens); I("mixed_steps", o.mixed_steps); I("prefill_max_wait_ms", o.prefill_max_wait_ms); I("tp", o.tp); I("tp_rank", o.tp_rank); I("tp_ar_bf16", o.tp_ar_bf16); I("tp_nvls", o.tp_nvls); I("tp_two_shot_rows", o.tp_two_shot_rows); o.tp_shm = j.s("tp_shm", o.tp_shm); o.tp_nonce = (uint64_t)j.i("tp_nonce", (int64_t)o.tp_nonce);
+    if (o.max_seq_len % 64) o.max_seq_len = (o.max_seq_len + 63) / 64 * 64;
+    if (m.arch == "ratasun") {
+        if (o.tp != 1) throw std::runtime_error("the hybrid model family runs with tp = 1");
+        return;
+    }
     if (m.hidden <= 0 || m.n_layers <= 0 || m.n_heads <= 0 || m.n_kv_heads <= 0 || m.ffn <= 0 || m.vocab <= 0)
         throw std::runtime_error("unknown model '" + name + "' and no explicit dimensions given");
     if (m.head_dim != 64 && m.head_dim != 128) throw std::runtime_error("head_dim must be 64 or 128");

@@ -55,12 +55,17 @@ struct Seq {
     std::chrono::steady_clock::time_point t_enqueue{};   // arrival (admission batching)
     bool preempted = false;                              // pushed back by the scheduler: re-admit without waiting
     bool cancelled = false;                              // oa_chat_cancel: dropped at the next step boundary
+    int state_slot = -1;                                 // slot of the recurrent state (models that carry one)
     int est_uncached = -1;                               // prompt tokens a prefill would have to compute (prefix-cache walk, made once)
 };
 
 class Engine {
 public:
-    Engine(const ModelConfig& mc, const EngineOptions& eo) : model_(mc, eo), tok_(mc, eo.tokenizer), opt_(eo) {
+    Engine(const ModelConfig& mc, const EngineOptions& eo) : model_p_(make_model(mc, eo)), model_(*model_p_), tok_(mc, eo.tokenizer), opt_(eo) {
+        if (model_.state_slots > 0) {          // recurrent state per sequence: one slot each, and no prefix reuse (a cached page cannot restore the state)
+            opt_.prefix_cache = 0;
+            for (int i = model_.state_slots - 1; i >= 0; --i) free_slots_.push_back(i);
+        }
         free_pages_.reserve(model_.num_pages);
         for (int p = model_.num_pages - 1; p >= 0; --p) free_pages_.push_back(p);
         page_ref_.assign(model_.num_pages, 0); page_hash_.assign(model_.num_pages, 0); page_parent_.assign(model_.num_pages, 0);
@@ -94,6 +99,8 @@ public:
         if ((int)prompt.size() + 1 > opt_.max_seq_len)
             return fail(OA_ERR_BAD_REQUEST, "prompt of " + std::to_string(prompt.size()) + " tokens exceeds max_seq_len " + std::to_string(opt_.max_seq_len));
         for (int32_t t : prompt) if (t < 0 || t >= model_.cfg.vocab) return fail(OA_ERR_BAD_REQUEST, "token id out of range");
+        if ((flags & (OA_FLAG_JSON_TOOLCALL | OA_FLAG_JSON_FINAL | OA_FLAG_JSON_FUNCTION | OA_FLAG_JSON_TEXT)) && model_.mask_slots == 0)
+            return fail(OA_ERR_BAD_REQUEST, "schema-constrained decoding is not available for this model");
         auto s = std::make_shared<Seq>();
         s->n_prompt = (int)prompt.size(); s->tokens = std::move(prompt);
         s->max_new = std::min(max_new, opt_.max_seq_len - s->n_prompt); s->flags = flags;
@@ -162,21 +169,94 @@ public:
         CallerDevice on_engine_device(opt_.device);      // this helper launches from the CALLER's thread
         try {
             const int V = model_.cfg.vocab;
-            std::vector<int32_t> pages;
-            { std::lock_guard<std::mutex> lk(mu_); if (!alloc_pages_locked(pages, (n + 63) / 64)) return fail(OA_ERR_OVERLOADED, "no free KV pages"); }
+            Seq tmp; tmp.tokens.assign(toks, toks + n);
+            {
+                std::lock_guard<std::mutex> lk(mu_);
+                if (model_.state_slots > 0) { if (free_slots_.empty()) return fail(OA_ERR_OVERLOADED, "no free state slot"); tmp.state_slot = free_slots_.back(); free_slots_.pop_back(); }
+                if (!alloc_pages_locked(tmp.pages, (n + 63) / 64)) { release_slot_locked(tmp); return fail(OA_ERR_OVERLOADED, "no free KV pages"); }
+            }
             float* d_logits = nullptr;
             cuda_check(cudaMalloc(&d_logits, (size_t)n * V * 4), "cudaMalloc logits");
-            StepInput in; in.decode = false; in.n_seqs = 1; in.want_logits = true;
-            in.block_tables.assign(model_.max_pages_per_seq, 0);
-            for (size_t i = 0; i < pages.size(); ++i) in.block_tables[i] = pages[i];
-            in.ctx_lens = {n};
-            for (int i = 0; i < n; ++i) { in.tokens.push_back(toks[i]); in.positions.push_back(i); in.slots.push_back(pages[i / 64] * 64 + i % 64); in.sample_rows.push_back(i); }
+            StepInput in; in.decode = false; in.want_logits = true;
+            append_rows_locked(in, tmp, 0, n);
+            for (int i = 0; i < n; ++i) in.sample_rows.push_back(i);
             for (int r = 0; r < n; r += PREFILL_TILE_ROWS) in.tiles.push_back(PrefillTile{0, r, r, std::min(PREFILL_TILE_ROWS, n - r)});
-            run_forward(in, d_logits); model_.sync();
-            cudaError_t e = cudaMemcpy(logits_out, d_logits, (size_t)n * V * 4, cudaMemcpyDeviceToHost);
+            cudaError_t e = cudaSuccess;
+            try { run_forward(in, d_logits); model_.sync(); e = cudaMemcpy(logits_out, d_logits, (size_t)n * V * 4, cudaMemcpyDeviceToHost); }
+            catch (...) { cudaFree(d_logits); std::lock_guard<std::mutex> lk(mu_); for (int p : tmp.pages) release_page_locked(p); release_slot_locked(tmp); throw; }
             cudaFree(d_logits);
-            { std::lock_guard<std::mutex> lk(mu_); for (int p : pages) release_page_locked(p); }
+            { std::lock_guard<std::mutex> lk(mu_); for (int p : tmp.pages) release_page_locked(p); release_slot_locked(tmp); }
             cuda_check(e, "logits D2H");
+        } catch (const std::exception& ex) { return fail(OA_ERR_INTERNAL, ex.what()); }
+        return OA_OK;
+    }
+
+    // Step-by-step replay of given token ids (the trace runner): every entry brings the next tokens of one request — a whole prompt, a portion
+    // of it or a single token — and all entries of a call run as ONE batch through the same forward, page allocator and state slots the
+    // scheduler uses.  Nothing is sampled; fp32 logits of the wanted rows come back.  Requests named in `end` give their pages and slot back.
+    int trace_step(int n_entries, const int64_t* ids, const int32_t* n_tokens, const int32_t* tokens, const int32_t* n_want, const int32_t* want, int n_end,
+                   const int64_t* end_ids, float* logits_out, int64_t cap_rows) {
+        std::lock_guard<std::mutex> step(step_mu_);
+        CallerDevice on_engine_device(opt_.device);
+        try {
+            const int V = model_.cfg.vocab;
+            StepInput in; in.decode = false; in.want_logits = true;
+            std::vector<std::shared_ptr<Seq>> batch; std::vector<int> take_of;
+            {
+                std::lock_guard<std::mutex> lk(mu_);
+                if (fatal_) return fail(OA_ERR_INTERNAL, "engine is in a failed state: " + fatal_msg_);
+                size_t tok_at = 0, want_at = 0;
+                for (int e = 0; e < n_entries; ++e) {
+                    const int take = n_tokens[e];
+                    if (take <= 0) return fail(OA_ERR_BAD_REQUEST, "trace entry without tokens");
+                    auto it = traced_.find(ids[e]);
+                    std::shared_ptr<Seq> s;
+                    if (it == traced_.end()) {
+                        if (model_.state_slots > 0 && free_slots_.empty()) return fail(OA_ERR_OVERLOADED, "no free state slot for a new request");
+                        s = std::make_shared<Seq>(); s->state = SeqState::PREFILL;
+                        if (model_.state_slots > 0) { s->state_slot = free_slots_.back(); free_slots_.pop_back(); }
+                        traced_[ids[e]] = s;
+                    } else s = it->second;
+                    for (size_t b = 0; b < batch.size(); ++b) if (batch[b] == s) return fail(OA_ERR_BAD_REQUEST, "a request appears twice in one step");
+                    for (int i = 0; i < take; ++i) { const int32_t t = tokens[tok_at + i]; if (t < 0 || t >= V) return fail(OA_ERR_BAD_REQUEST, "token id out of range"); s->tokens.push_back(t); }
+                    tok_at += (size_t)take;
+                    if ((int)s->tokens.size() > opt_.max_seq_len) return fail(OA_ERR_BAD_REQUEST, "request longer than max_seq_len");
+                    const int need = ((int)s->tokens.size() + 63) / 64 - (int)s->pages.size();
+                    if (need > 0 && !alloc_pages_locked(s->pages, need)) return fail(OA_ERR_OVERLOADED, "no free cache pages");
+                    const int row0 = (int)in.tokens.size();
+                    const int sidx = append_rows_locked(in, *s, s->n_cached, take);
+                    for (int r = 0; r < take; r += PREFILL_TILE_ROWS) in.tiles.push_back(PrefillTile{sidx, row0 + r, s->n_cached + r, std::min(PREFILL_TILE_ROWS, take - r)});
+                    for (int k = 0; k < n_want[e]; ++k) {
+                        const int wpos = want[want_at + k];
+                        if (wpos < 0 || wpos >= take) return fail(OA_ERR_BAD_REQUEST, "wanted place outside the entry's tokens");
+                        in.sample_rows.push_back(row0 + wpos);
+                    }
+                    want_at += (size_t)n_want[e];
+                    batch.push_back(s); take_of.push_back(take);
+                }
+            }
+            const size_t n_rows = in.sample_rows.size();
+            if ((int64_t)n_rows > cap_rows) return fail(OA_ERR_BAD_REQUEST, "logits buffer too small");
+            if (!in.tokens.empty()) {
+                if (n_rows * (size_t)V > trace_logits_cap_) {
+                    if (trace_logits_) cudaFree(trace_logits_);
+                    trace_logits_ = nullptr; trace_logits_cap_ = 0;
+                    cuda_check(cudaMalloc(&trace_logits_, n_rows * (size_t)V * 4), "cudaMalloc logits");
+                    trace_logits_cap_ = n_rows * (size_t)V;
+                }
+                run_forward(in, n_rows ? trace_logits_ : nullptr); model_.sync();
+                if (n_rows) cuda_check(cudaMemcpy(logits_out, trace_logits_, n_rows * (size_t)V * 4, cudaMemcpyDeviceToHost), "logits D2H");
+            }
+            {
+                std::lock_guard<std::mutex> lk(mu_);
+                for (size_t b = 0; b < batch.size(); ++b) batch[b]->n_cached += take_of[b];
+                n_prefill_tokens_ += in.tokens.size(); ++n_prefill_steps_;
+                for (int k = 0; k < n_end; ++k) {
+                    auto it = traced_.find(end_ids[k]);
+                    if (it == traced_.end()) continue;
+                    finish_locked(it->second, 0); traced_.erase(it);
+                }
+            }
         } catch (const std::exception& ex) { return fail(OA_ERR_INTERNAL, ex.what()); }
         return OA_OK;
     }
@@ -190,13 +270,19 @@ public:
             const int V = model_.cfg.vocab;
             const int total_len = ctx_len + steps + warmup;
             const int pages_per = (total_len + 63) / 64;
-            std::vector<std::vector<int32_t>> pages(batch);
+            std::vector<Seq> seqs(batch);
+            auto synth = [&](int b, int i) { uint64_t h = (uint64_t)(b + 1) * 0x9E3779B97F4A7C15ull + (uint64_t)i * 0xBF58476D1CE4E5B9ull; h ^= h >> 29; return (int32_t)(h % (uint64_t)V); };
             {
                 std::lock_guard<std::mutex> lk(mu_);
                 if ((long long)pages_per * batch > (long long)available_pages_locked()) return fail(OA_ERR_OVERLOADED, "bench_decode: not enough KV pages");
-                for (int b = 0; b < batch; ++b) alloc_pages_locked(pages[b], pages_per);
+                if (model_.state_slots > 0 && (int)free_slots_.size() < batch) return fail(OA_ERR_OVERLOADED, "bench_decode: not enough state slots");
+                for (int b = 0; b < batch; ++b) {
+                    alloc_pages_locked(seqs[b].pages, pages_per);
+                    if (model_.state_slots > 0) { seqs[b].state_slot = free_slots_.back(); free_slots_.pop_back(); }
+                    seqs[b].tokens.resize(ctx_len);
+                    for (int i = 0; i < ctx_len; ++i) seqs[b].tokens[i] = synth(b, i);
+                }
             }
-            auto synth = [&](int b, int i) { uint64_t h = (uint64_t)(b + 1) * 0x9E3779B97F4A7C15ull + (uint64_t)i * 0xBF58476D1CE4E5B9ull; h ^= h >> 29; return (int32_t)(h % (uint64_t)V); };
             cudaEvent_t e0, e1; cudaEventCreate(&e0); cudaEventCreate(&e1);
             const bool prof_all = model_.profile_all; model_.profile_all = false;      // in-situ kernel timing covers the decode steps only
             // ---- prefill: ctx_len-1 tokens per sequence, chunked by the step token budget ----
@@ -211,12 +297,8 @@ public:
                     int budget = opt_.max_step_tokens;
                     while (b < batch && budget > 0 && in.n_seqs < opt_.max_batch) {
                         const int take = std::min(budget, P - off);
-                        const int sidx = in.n_seqs++;
-                        in.block_tables.resize((size_t)in.n_seqs * model_.max_pages_per_seq, 0);
-                        for (size_t i = 0; i < pages[b].size(); ++i) in.block_tables[(size_t)sidx * model_.max_pages_per_seq + i] = pages[b][i];
-                        in.ctx_lens.push_back(off + take);
                         const int row0 = (int)in.tokens.size();
-                        for (int i = off; i < off + take; ++i) { in.tokens.push_back(synth(b, i)); in.positions.push_back(i); in.slots.push_back(pages[b][i / 64] * 64 + i % 64); }
+                        const int sidx = append_rows_locked(in, seqs[b], off, take);
                         for (int r = 0; r < take; r += PREFILL_TILE_ROWS) in.tiles.push_back(PrefillTile{sidx, row0 + r, off + r, std::min(PREFILL_TILE_ROWS, take - r)});
                         budget -= take; off += take;
                         if (off >= P) { off = 0; ++b; }
@@ -238,12 +320,10 @@ public:
             model_.attn_ms_accum = 0;
             for (int it = 0; it < warmup + steps; ++it) {
                 const int pos = P + it;
-                StepInput in; in.decode = true; in.n_seqs = batch;
-                in.block_tables.assign((size_t)batch * model_.max_pages_per_seq, 0);
+                StepInput in; in.decode = true;
                 for (int b = 0; b < batch; ++b) {
-                    for (size_t i = 0; i < pages[b].size(); ++i) in.block_tables[(size_t)b * model_.max_pages_per_seq + i] = pages[b][i];
-                    in.tokens.push_back(last[b]); in.positions.push_back(pos); in.slots.push_back(pages[b][pos / 64] * 64 + pos % 64);
-                    in.ctx_lens.push_back(pos + 1); in.sample_rows.push_back(b);
+                    seqs[b].tokens.resize((size_t)pos + 1); seqs[b].tokens[pos] = last[b];
+                    append_rows_locked(in, seqs[b], pos, 1); in.sample_rows.push_back(b);
                 }
                 if (it == warmup) {
                     if (std::getenv("OA_CUDA_PROFILER")) { model_.sync(); cudaProfilerStart(); }   // ncu --profile-from-start off
@@ -262,7 +342,7 @@ public:
             float bracket_ms = 0; cudaEventElapsedTime(&bracket_ms, eb0, eb1);
             const uint64_t launches1 = launches_total();
             cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(eb0); cudaEventDestroy(eb1);
-            { std::lock_guard<std::mutex> lk(mu_); for (auto& pv : pages) for (int p : pv) release_page_locked(p); }
+            { std::lock_guard<std::mutex> lk(mu_); for (auto& q : seqs) { for (int p : q.pages) release_page_locked(p); release_slot_locked(q); } }
             const double mean_ctx = ctx_sum / steps;
             out[0] = bracket_ms / steps; if (n_out > 6) out[6] = total_ms / steps; out[1] = prefill_ms; out[2] = (double)(launches1 - launches0) / steps; out[3] = mean_ctx;
             out[4] = model_.profile_attn ? model_.attn_ms_accum / steps : 0.0;
@@ -315,7 +395,7 @@ public:
     const Tokenizer& tokenizer() const { return tok_; }
     const EngineOptions& options() const { return opt_; }
     const ModelConfig& config() const { return model_.cfg; }
-    DeviceModel& model() { return model_; }
+    ModelBase& model() { return model_; }
 
 private:
     // every forward goes through here: the leader of a tensor-parallel group publishes the step for its followers first
@@ -413,10 +493,22 @@ private:
             s->hash_prev = hi; s->n_registered = i + 1;
         }
     }
+    void release_slot_locked(Seq& s) { if (s.state_slot >= 0) { free_slots_.push_back(s.state_slot); s.state_slot = -1; } }
+    // rows [start, start + take) of s as one sequence of the step: ids, positions, cache slots, block-table row, its rows' range and state slot
+    int append_rows_locked(StepInput& in, const Seq& s, int start, int take) {
+        const int sidx = in.n_seqs++;
+        in.block_tables.resize((size_t)in.n_seqs * model_.max_pages_per_seq, 0);
+        for (size_t i = 0; i < s.pages.size(); ++i) in.block_tables[(size_t)sidx * model_.max_pages_per_seq + i] = s.pages[i];
+        in.ctx_lens.push_back(start + take);
+        if (in.seq_row0.empty()) in.seq_row0.push_back(0);
+        for (int i = start; i < start + take; ++i) { in.tokens.push_back(s.tokens[i]); in.positions.push_back(i); in.slots.push_back(s.pages[i / 64] * 64 + i % 64); }
+        in.seq_row0.push_back((int32_t)in.tokens.size()); in.state_slots.push_back(s.state_slot);
+        return sidx;
+    }
     void finish_locked(const std::shared_ptr<Seq>& s, int reason) {
         s->finish_reason = reason; s->state = SeqState::DONE; s->done = true;
         for (int p : s->pages) release_page_locked(p);
-        s->pages.clear(); ++n_completed_;
+        s->pages.clear(); release_slot_locked(*s); ++n_completed_;
     }
     // Accept a sampled token for s (called with mu_ held). Returns true if the sequence finished.
     bool accept_token_locked(const std::shared_ptr<Seq>& s, int32_t t) {
@@ -520,6 +612,7 @@ private:
                 auto& s = waiting_.front();
                 const int need = ((int)s->tokens.size() + 1 + 63) / 64;
                 if (need > model_.num_pages) { s->error = OA_ERR_BAD_REQUEST; s->error_msg = "request larger than the KV pool"; s->done = true; waiting_.pop_front(); cv_done_.notify_all(); continue; }
+                if (model_.state_slots > 0 && free_slots_.empty()) break;   // no state slot free: wait for a sequence to finish
                 match_prefix_locked(s);                                   // cached prefix pages (ref-counted), s->n_cached set
                 if (!alloc_pages_locked(s->pages, need - (int)s->pages.size())) {
                     for (int p : s->pages) release_page_locked(p);
@@ -527,6 +620,7 @@ private:
                     break;
                 }
                 s->state = SeqState::PREFILL; s->preempted = false;
+                if (model_.state_slots > 0) { s->state_slot = free_slots_.back(); free_slots_.pop_back(); }
                 running_.push_back(s); waiting_.pop_front();
             }
             if (running_.empty()) return;
@@ -543,12 +637,8 @@ private:
                         if (s->state != SeqState::DECODE || budget <= 1) continue;
                         const int pos = (int)s->tokens.size() - 1;
                         if (pos / 64 >= (int)s->pages.size() && !alloc_pages_locked(s->pages, 1)) continue;
-                        const int sidx = in.n_seqs++;
-                        in.block_tables.resize((size_t)in.n_seqs * model_.max_pages_per_seq, 0);
-                        for (size_t i = 0; i < s->pages.size(); ++i) in.block_tables[(size_t)sidx * model_.max_pages_per_seq + i] = s->pages[i];
-                        in.ctx_lens.push_back(pos + 1);
                         in.sample_rows.push_back((int)in.tokens.size());
-                        in.tokens.push_back(s->tokens[pos]); in.positions.push_back(pos); in.slots.push_back(s->pages[pos / 64] * 64 + pos % 64);
+                        append_rows_locked(in, *s, pos, 1);
                         batch.push_back(s); take_of.push_back(0); sampled.push_back(s); --budget;
                     }
                     in.n_decode = in.n_seqs;
@@ -557,14 +647,8 @@ private:
                     if (s->state != SeqState::PREFILL || budget <= 0) continue;
                     const int remaining = (int)s->tokens.size() - s->n_cached;
                     const int take = std::min(remaining, budget);
-                    const int sidx = in.n_seqs++;
-                    in.block_tables.resize((size_t)in.n_seqs * model_.max_pages_per_seq, 0);
-                    for (size_t i = 0; i < s->pages.size(); ++i) in.block_tables[(size_t)sidx * model_.max_pages_per_seq + i] = s->pages[i];
-                    in.ctx_lens.push_back(s->n_cached + take);
                     const int row0 = (int)in.tokens.size();
-                    for (int i = s->n_cached; i < s->n_cached + take; ++i) {
-                        in.tokens.push_back(s->tokens[i]); in.positions.push_back(i); in.slots.push_back(s->pages[i / 64] * 64 + i % 64);
-                    }
+                    const int sidx = append_rows_locked(in, *s, s->n_cached, take);
                     for (int r = 0; r < take; r += PREFILL_TILE_ROWS) in.tiles.push_back(PrefillTile{sidx, row0 + r, s->n_cached + r, std::min(PREFILL_TILE_ROWS, take - r)});
                     if (take == remaining) { in.sample_rows.push_back(row0 + take - 1); sampled.push_back(s); }
                     batch.push_back(s); take_of.push_back(take); budget -= take;
@@ -574,6 +658,7 @@ private:
                 // every decoding sequence needs a slot for its newest token; preempt (recompute later) if the pool is dry
                 auto preempt = [&](const std::shared_ptr<Seq>& v) {
                     for (int p : v->pages) release_page_locked(p);
+                    release_slot_locked(*v);             // recompute restarts at position 0, where the state is taken as zero
                     v->pages.clear(); v->n_cached = 0; v->state = SeqState::WAITING; v->preempted = true;
                     waiting_.push_front(v); ++n_preempt_;
                 };
@@ -588,14 +673,10 @@ private:
                     ++i;
                 }
                 if (running_.empty()) return;
-                in.n_seqs = (int)running_.size();
-                in.block_tables.assign((size_t)in.n_seqs * model_.max_pages_per_seq, 0);
                 for (size_t b = 0; b < running_.size(); ++b) {
                     auto& s = running_[b];
-                    const int pos = (int)s->tokens.size() - 1;
-                    for (size_t i = 0; i < s->pages.size(); ++i) in.block_tables[b * model_.max_pages_per_seq + i] = s->pages[i];
-                    in.tokens.push_back(s->tokens[pos]); in.positions.push_back(pos); in.slots.push_back(s->pages[pos / 64] * 64 + pos % 64);
-                    in.ctx_lens.push_back(pos + 1); in.sample_rows.push_back((int)b);
+                    append_rows_locked(in, *s, (int)s->tokens.size() - 1, 1);
+                    in.sample_rows.push_back((int)b);
                     batch.push_back(s); sampled.push_back(s);
                 }
             }
@@ -643,7 +724,10 @@ private:
         }
     }
 
-    DeviceModel model_; Tokenizer tok_; EngineOptions opt_;
+    std::unique_ptr<ModelBase> model_p_; ModelBase& model_; Tokenizer tok_; EngineOptions opt_;
+    float* trace_logits_ = nullptr; size_t trace_logits_cap_ = 0;
+    std::vector<int32_t> free_slots_;              // state slots of models with per-sequence recurrent state
+    std::unordered_map<int64_t, std::shared_ptr<Seq>> traced_;      // sequences driven step by step through trace_step()
     std::mutex mu_, step_mu_;
     std::condition_variable cv_work_, cv_done_;
     std::deque<std::shared_ptr<Seq>> waiting_;
@@ -789,10 +873,10 @@ int oa_bench_decode(oa_engine* h, int32_t batch, int32_t ctx_len, int32_t steps,
 }
 int oa_debug_kernel_times(oa_engine* h, char* buf, size_t n, int32_t reset) {
     if (!h || !buf) return fail(OA_ERR_BAD_REQUEST, "null argument");
-    DeviceModel& m = h->e->model();
+    ModelBase& m = h->e->model();
     std::string s = "{";
     for (int i = 0; i < 14; ++i) {
-        char t[128]; std::snprintf(t, sizeof t, "%s\"%s\": [%.4f, %ld]", i ? ", " : "", DeviceModel::kt_name(i), m.kt_ms[i], m.kt_n[i]); s += t;
+        char t[128]; std::snprintf(t, sizeof t, "%s\"%s\": [%.4f, %ld]", i ? ", " : "", ModelBase::kt_name(i), m.kt_ms[i], m.kt_n[i]); s += t;
         if (reset) { m.kt_ms[i] = 0; m.kt_n[i] = 0; }
     }
     s += "}";
@@ -829,6 +913,11 @@ int oa_host_bpe_decode(const char* tokenizer_json_path, const int32_t* ids, int3
     return OA_OK;
 }
 
+int oa_trace_step(oa_engine* h, int32_t n_entries, const int64_t* ids, const int32_t* n_tokens, const int32_t* tokens, const int32_t* n_want, const int32_t* want,
+                  int32_t n_end, const int64_t* end_ids, float* logits_out, int64_t logits_cap_rows) {
+    if (!h || n_entries < 0 || n_end < 0 || (n_entries > 0 && (!ids || !n_tokens || !tokens || !n_want))) return fail(OA_ERR_BAD_REQUEST, "null argument");
+    return h->e->trace_step(n_entries, ids, n_tokens, tokens, n_want, want, n_end, end_ids, logits_out, logits_cap_rows);
+}
 int oa_engine_serve(oa_engine* h) { if (!h) return fail(OA_ERR_BAD_REQUEST, "null engine"); return h->e->serve(); }
 uint64_t oa_kernel_launches(void) { return launches_total(); }
 const char* oa_version(void) { return "opsagent_b200 0.1 (sm_100a)"; }

@@ -1,0 +1,611 @@
+// hybrid_kernels.cu — see hybrid_kernels.hpp.  Plain CUDA kernels, one per mechanism, written for any sizes a configuration may give.
+// TA is the activation / matrix element type (__nv_bfloat16 or float); all arithmetic is fp32.
+#include <cuda_bf16.h>
+#include <math.h>
+
+#include "hybrid_kernels.hpp"
+#include "kernels.hpp"
+
+namespace oa {
+
+namespace {
+
+__device__ __forceinline__ float ldf(const float* p) { return *p; }
+__device__ __forceinline__ float ldf(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void stf(float* p, float v) { *p = v; }
+__device__ __forceinline__ void stf(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float siluf_(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplusf_(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+// sum over the block (blockDim.x <= 1024, a multiple of 32); every thread gets the result
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (l == 0) red[w] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int i = 0; i < nw; ++i) t += red[i];
+    return t;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_plain(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    count_launch();
+    kern<<<grid, block, smem, st>>>(KArgs(args)...);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// GEMM: 64 x 64 tile, 16-wide k slices, 256 threads x (4 x 4) outputs.  The k order of every output is fixed (0..K-1), so a row's result
+// does not depend on which other rows share its launch.
+// ---------------------------------------------------------------------------------------------------------------------------------
+template <typename TA, int MODE>
+__global__ void __launch_bounds__(256) hy_gemm_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ B, int ldb, void* Cv, int ldc, int M, int N, int K,
+                                                      const float* __restrict__ bias, float alpha, long long sA, long long sB, long long sC) {
+    __shared__ float As[16][64 + 4], Bs[16][64 + 4];
+    A += (long long)blockIdx.z * sA; B += (long long)blockIdx.z * sB;
+    const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64, tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += 16) {
+        for (int i = tid; i < 64 * 16; i += 256) {
+            const int r = i >> 4, k = i & 15;
+            As[k][r] = (m0 + r < M && k0 + k < K) ? ldf(A + (long long)(m0 + r) * lda + k0 + k) : 0.f;
+            Bs[k][r] = (n0 + r < N && k0 + k < K) ? ldf(B + (long long)(n0 + r) * ldb + k0 + k) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { a[i] = As[k][ty * 4 + i]; b[i] = Bs[k][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v = acc[i][j] * alpha + (bias ? bias[n] : 0.f);
+            const long long at = (long long)blockIdx.z * sC + (long long)m * ldc + n;
+            if (MODE == HY_STORE) stf(reinterpret_cast<TA*>(Cv) + at, v);
+            else if (MODE == HY_STORE_F32) reinterpret_cast<float*>(Cv)[at] = v;
+            else reinterpret_cast<float*>(Cv)[at] += v;
+        }
+    }
+}
+
+template <typename TA>
+__global__ void hy_embed_kernel(const int32_t* ids, const TA* table, float* x, float* x0, int T, int W, int vocab) {
+    const int t = blockIdx.x; int id = ids[t]; id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) { const float v = ldf(table + (long long)id * W + c); x[(long long)t * W + c] = v; x0[(long long)t * W + c] = v; }
+}
+template <typename TA>
+__global__ void hy_concat_kernel(const float* x, const float* x0, TA* cat, int T, int W) {
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) { stf(cat + (long long)t * 2 * W + c, x[(long long)t * W + c]); stf(cat + (long long)t * 2 * W + W + c, x0[(long long)t * W + c]); }
+}
+template <typename TA>
+__global__ void __launch_bounds__(256) hy_layernorm_kernel(const float* x, const int32_t* rows, const float* w, TA* out, int ldo, int W, float eps) {
+    __shared__ float red[32];
+    const int t = blockIdx.x; const float* xr = x + (long long)(rows ? rows[t] : t) * W;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) s += xr[c];
+    const float mean = block_sum(s, red) / (float)W;
+    float v = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) { const float d = xr[c] - mean; v += d * d; }
+    const float rstd = 1.0f / sqrtf(block_sum(v, red) / (float)W + eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) stf(out + (long long)t * ldo + c, (xr[c] - mean) * rstd * w[c]);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// latent attention
+// ---------------------------------------------------------------------------------------------------------------------------------
+template <typename TA>
+__global__ void __launch_bounds__(128) hy_mla_prep_kernel(HyLatentAttn a, const TA* q, int ldq, const TA* ckv, int ldc, const float* norm_w, float eps,
+                                                           const float* rope_cos, const float* rope_sin, TA* cache, float* q_abs, HyRows r) {
+    __shared__ float red[32];
+    const int t = blockIdx.x, R = a.kv_rank, rot = a.rot_dim, half = a.rot_dims / 2, E = R + rot;
+    const TA* c = ckv + (long long)t * ldc;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < R; i += blockDim.x) { const float v = ldf(c + i); ss += v * v; }
+    const float rr = 1.0f / sqrtf(block_sum(ss, red) / (float)R + eps);
+    TA* dst = cache + (long long)r.slots[t] * E;
+    for (int i = threadIdx.x; i < R; i += blockDim.x) stf(dst + i, ldf(c + i) * rr * norm_w[i]);
+    const int pos = r.positions[t];
+    const float* cs = rope_cos + (long long)pos * half; const float* sn = rope_sin + (long long)pos * half;
+    for (int i = threadIdx.x; i < rot; i += blockDim.x) {          // shared rotated key
+        float v;
+        if (i < 2 * half) { const int p = i >> 1; const float u0 = ldf(c + R + 2 * p), u1 = ldf(c + R + 2 * p + 1); v = (i & 1) ? (u1 * cs[p] + u0 * sn[p]) : (u0 * cs[p] - u1 * sn[p]); }
+        else v = ldf(c + R + i);
+        stf(dst + R + i, v);
+    }
+    for (int i = threadIdx.x; i < a.heads * rot; i += blockDim.x) {   // rotated query parts
+        const int h = i / rot, d = i - h * rot; const TA* qh = q + (long long)t * ldq + (long long)h * (a.dim + rot) + a.dim;
+        float v;
+        if (d < 2 * half) { const int p = d >> 1; const float u0 = ldf(qh + 2 * p), u1 = ldf(qh + 2 * p + 1); v = (d & 1) ? (u1 * cs[p] + u0 * sn[p]) : (u0 * cs[p] - u1 * sn[p]); }
+        else v = ldf(qh + d);
+        q_abs[((long long)t * a.heads + h) * E + R + d] = v;
+    }
+}
+
+constexpr int MLA_ACC = 16;     // latent channels per lane: kv_rank <= 32 * MLA_ACC
+template <typename TA>
+__global__ void __launch_bounds__(128) hy_mla_attention_kernel(HyLatentAttn a, const float* q_abs, const TA* cache, TA* lat_out, HyRows r) {
+    extern __shared__ float sm[];
+    const int t = blockIdx.x, h = blockIdx.y, R = a.kv_rank, E = R + a.rot_dim;
+    float* qs = sm;                      // [E]
+    float* macc = sm + E;                // [4][R] partial outputs, then [4] m, [4] l
+    float* mm = macc + 4 * R; float* ll = mm + 4;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float* qr = q_abs + ((long long)t * a.heads + h) * E;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) qs[i] = qr[i] * a.scale;
+    __syncthreads();
+    const int seq = r.row_seq[t], pos = r.positions[t];
+    const int32_t* bt = r.block_tables + (long long)seq * r.max_pages_per_seq;
+    float m = -INFINITY, l = 0.f, acc[MLA_ACC];
+#pragma unroll
+    for (int i = 0; i < MLA_ACC; ++i) acc[i] = 0.f;
+    for (int j = warp; j <= pos; j += 4) {
+        const TA* kr = cache + ((long long)bt[j >> 6] * 64 + (j & 63)) * E;
+        float d = 0.f;
+        for (int i = lane; i < E; i += 32) d = fmaf(qs[i], ldf(kr + i), d);
+        d = warp_sum(d);
+        const float mn = fmaxf(m, d), corr = expf(m - mn), p = expf(d - mn);
+        l = l * corr + p; m = mn;
+#pragma unroll
+        for (int i = 0; i < MLA_ACC; ++i) { const int c = lane + 32 * i; if (c < R) acc[i] = acc[i] * corr + p * ldf(kr + c); }
+    }
+#pragma unroll
+    for (int i = 0; i < MLA_ACC; ++i) { const int c = lane + 32 * i; if (c < R) macc[warp * R + c] = acc[i]; }
+    if (lane == 0) { mm[warp] = m; ll[warp] = l; }
+    __syncthreads();
+    float M = fmaxf(fmaxf(mm[0], mm[1]), fmaxf(mm[2], mm[3])), L = 0.f, f[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) { f[w] = mm[w] == -INFINITY ? 0.f : expf(mm[w] - M); L += f[w] * ll[w]; }
+    const float inv = 1.0f / L;
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) v += f[w] * macc[w * R + c];
+        stf(lat_out + ((long long)t * a.heads + h) * R + c, v * inv);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// short causal convolution with carried tails
+// ---------------------------------------------------------------------------------------------------------------------------------
+template <typename TA>
+__device__ __forceinline__ float conv_input(const TA* in, int ld_in, int C, const TA* tail, int taps, int row0, int pos0, int src, int c) {
+    if (src >= 0) return ldf(in + (long long)(row0 + src) * ld_in + c);
+    if (pos0 <= 0) return 0.f;
+    return ldf(tail + (long long)(taps - 1 + src) * C + c);
+}
+template <typename TA>
+__global__ void hy_conv_silu_kernel(const TA* in, int ld_in, int C, const float* w, const float* bias, int taps, TA* out, int ld_out, const TA* tails, HyRows r) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (c >= C) return;
+    const int seq = r.row_seq[t], row0 = r.seq_row0[seq], i = t - row0, pos0 = r.seq_pos0[seq];
+    const TA* tail = tails + (long long)r.seq_state[seq] * (taps - 1) * C;
+    float acc = bias ? bias[c] : 0.f;
+    for (int j = 0; j < taps; ++j) acc = fmaf(w[c * taps + j], conv_input(in, ld_in, C, tail, taps, row0, pos0, i - (taps - 1) + j, c), acc);
+    stf(out + (long long)t * ld_out + c, siluf_(acc));
+}
+template <typename TA>
+__global__ void hy_conv_tails_kernel(const TA* in, int ld_in, int C, int taps, TA* tails, HyRows r) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, seq = blockIdx.y;
+    if (c >= C) return;
+    const int row0 = r.seq_row0[seq], len = r.seq_row0[seq + 1] - row0, pos0 = r.seq_pos0[seq];
+    TA* tail = tails + (long long)r.seq_state[seq] * (taps - 1) * C;
+    float v[16];
+    for (int j = 0; j < taps - 1; ++j) v[j] = conv_input(in, ld_in, C, tail, taps, row0, pos0, len - (taps - 1) + j, c);
+    for (int j = 0; j < taps - 1; ++j) stf(tail + (long long)j * C + c, v[j]);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// recurrences
+// ---------------------------------------------------------------------------------------------------------------------------------
+template <typename TA>
+__global__ void __launch_bounds__(128) hy_delta_prep_kernel(HyDelta d, const TA* conv, int ld_conv, const TA* b, int ld_b, const TA* a, int ld_a, const float* A_log,
+                                                             const float* dt_bias, float* qq, float* kk, float* vv, float* dec, float* beta) {
+    const int t = blockIdx.x, KH = d.kv_heads, H = d.heads, D = d.dim, VD = d.vdim;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const TA* cr = conv + (long long)t * ld_conv;
+    for (int u = warp; u < 2 * KH; u += 4) {                    // unit vectors per q / k head
+        const TA* src = cr + (long long)u * D;                   // q heads then k heads, contiguous
+        float ss = 0.f;
+        for (int i = lane; i < D; i += 32) { const float v = ldf(src + i); ss += v * v; }
+        ss = warp_sum(ss);
+        const float sc = (u < KH ? rsqrtf((float)D) : 1.0f) / sqrtf(ss + 1e-6f);
+        float* dst = (u < KH ? qq + ((long long)t * KH + u) * D : kk + ((long long)t * KH + (u - KH)) * D);
+        for (int i = lane; i < D; i += 32) dst[i] = ldf(src + i) * sc;
+    }
+    for (int i = threadIdx.x; i < H * VD; i += blockDim.x) vv[(long long)t * H * VD + i] = ldf(cr + 2 * KH * D + i);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) beta[(long long)t * H + i] = sigmoidf_(ldf(b + (long long)t * ld_b + i));
+    for (int i = threadIdx.x; i < H * D; i += blockDim.x)
+        dec[(long long)t * H * D + i] = expf(-expf(A_log[i / D]) * softplusf_(ldf(a + (long long)t * ld_a + i) + dt_bias[i]));
+}
+template <typename TA>
+__global__ void __launch_bounds__(128) hy_mamba_prep_kernel(HyMamba m, const TA* conv, int ld_conv, const TA* dt, int ld_dt, const float* A_log, const float* dt_bias,
+                                                             float* qq, float* kk, float* vv, float* dec) {
+    const int t = blockIdx.x, H = m.heads, VD = m.vdim, N = m.state, G = m.groups, inner = H * VD;
+    const TA* cr = conv + (long long)t * ld_conv;
+    for (int i = threadIdx.x; i < G * N; i += blockDim.x) { kk[(long long)t * G * N + i] = ldf(cr + inner + i); qq[(long long)t * G * N + i] = ldf(cr + inner + G * N + i); }
+    for (int i = threadIdx.x; i < inner; i += blockDim.x) {
+        const int h = i / VD; const float step = softplusf_(ldf(dt + (long long)t * ld_dt + h) + dt_bias[h]);
+        vv[(long long)t * inner + i] = step * ldf(cr + i);
+    }
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float step = softplusf_(ldf(dt + (long long)t * ld_dt + h) + dt_bias[h]);
+        dec[(long long)t * H + h] = expf(-expf(A_log[h]) * step);
+    }
+}
+
+constexpr int REC_COLS = 64;      // state columns (value channels) per CTA; a column evolves independently of the others
+template <bool DELTA>
+__global__ void __launch_bounds__(REC_COLS) hy_recurrence_kernel(const float* qq, const float* kk, const float* vv, const float* dec, const float* beta, float* out,
+                                                                 float* state, int H, int QH, int D, int VD, HyRows r) {
+    extern __shared__ float sm[];
+    float* S = sm;                         // [D][REC_COLS]
+    float* qs = S + D * REC_COLS; float* ks = qs + D; float* ds = ks + D;
+    const int seq = blockIdx.x, h = blockIdx.y, col = blockIdx.z * REC_COLS + threadIdx.x, j = threadIdx.x;
+    const bool ok = col < VD;
+    const int row0 = r.seq_row0[seq], len = r.seq_row0[seq + 1] - row0, pos0 = r.seq_pos0[seq], qh = h / (H / QH);
+    float* st = state + ((long long)r.seq_state[seq] * H + h) * D * VD;
+    for (int d = 0; d < D; ++d) S[d * REC_COLS + j] = (ok && pos0 > 0) ? st[(long long)d * VD + col] : 0.f;
+    for (int i = 0; i < len; ++i) {
+        const long long t = row0 + i;
+        __syncthreads();
+        for (int d = j; d < D; d += REC_COLS) {
+            qs[d] = qq[(t * QH + qh) * D + d]; ks[d] = kk[(t * QH + qh) * D + d];
+            if (DELTA) ds[d] = dec[(t * H + h) * D + d];
+        }
+        __syncthreads();
+        const float v = ok ? vv[(t * H + h) * VD + col] : 0.f;
+        float o = 0.f;
+        if (DELTA) {
+            float dot = 0.f;
+            for (int d = 0; d < D; ++d) { const float s = S[d * REC_COLS + j] * ds[d]; S[d * REC_COLS + j] = s; dot = fmaf(s, ks[d], dot); }
+            const float u = beta[t * H + h] * (v - dot);
+            for (int d = 0; d < D; ++d) { const float s = fmaf(ks[d], u, S[d * REC_COLS + j]); S[d * REC_COLS + j] = s; o = fmaf(s, qs[d], o); }
+        } else {
+            const float a = dec[t * H + h];
+            for (int d = 0; d < D; ++d) { const float s = fmaf(ks[d], v, S[d * REC_COLS + j] * a); S[d * REC_COLS + j] = s; o = fmaf(s, qs[d], o); }
+        }
+        if (ok) out[(t * H + h) * VD + col] = o;
+    }
+    if (ok) for (int d = 0; d < D; ++d) st[(long long)d * VD + col] = S[d * REC_COLS + j];
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(128) hy_gated_norm_kernel(const float* o, int C, int group, const float* w, int wlen, const TA* gate, int ld_gate, int gate_before, int act,
+                                                             const float* skip, int skip_block, const TA* xs, int ld_xs, TA* out, int ld_out, float eps) {
+    __shared__ float red[32];
+    const int t = blockIdx.x, c0 = blockIdx.y * group;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < group; i += blockDim.x) {
+        const int c = c0 + i;
+        float v = o[(long long)t * C + c];
+        if (skip) v = fmaf(skip[c / skip_block], ldf(xs + (long long)t * ld_xs + c), v);
+        if (gate_before) { const float g = ldf(gate + (long long)t * ld_gate + c); v *= act ? siluf_(g) : sigmoidf_(g); }
+        ss += v * v;
+    }
+    const float rr = 1.0f / sqrtf(block_sum(ss, red) / (float)group + eps);
+    for (int i = threadIdx.x; i < group; i += blockDim.x) {
+        const int c = c0 + i;
+        float v = o[(long long)t * C + c];
+        if (skip) v = fmaf(skip[c / skip_block], ldf(xs + (long long)t * ld_xs + c), v);
+        const float g = ldf(gate + (long long)t * ld_gate + c), ga = act ? siluf_(g) : sigmoidf_(g);
+        if (gate_before) v *= ga;
+        v = v * rr * w[c % wlen];
+        if (!gate_before) v *= ga;
+        stf(out + (long long)t * ld_out + c, v);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// mixture of experts
+// ---------------------------------------------------------------------------------------------------------------------------------
+// arg-max over the warp: larger value wins, equal values -> lower index
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o); const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+    }
+}
+template <typename TA>
+__global__ void __launch_bounds__(128) hy_moe_router_kernel(HyRouter m, const TA* h, int ldh, const TA* wr, int ldw, const float* correction, int W, int32_t* idx, float* wgt) {
+    extern __shared__ float sm[];
+    const int E = m.experts, G = m.groups, per = E / G;
+    float* sc = sm;               // [E] sigmoid scores
+    float* ch = sm + E;           // [E] choice scores (masked: -inf)
+    float* gs = ch + E;           // [G] group scores
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const TA* hr = h + (long long)t * ldh;
+    for (int e = warp; e < E; e += 4) {
+        float d = 0.f;
+        for (int i = lane; i < W; i += 32) d = fmaf(ldf(hr + i), ldf(wr + (long long)e * ldw + i), d);
+        d = warp_sum(d);
+        if (lane == 0) { const float s = sigmoidf_(d); sc[e] = s; ch[e] = s + correction[e]; }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    if (G > 1 && m.keep < G) {
+        for (int g = lane; g < G; g += 32) {                     // a group's score: the sum of its two largest choice scores
+            float a = -INFINITY, b = -INFINITY;
+            for (int i = 0; i < per; ++i) { const float v = ch[g * per + i]; if (v > a) { b = a; a = v; } else if (v > b) b = v; }
+            gs[g] = per >= 2 ? a + b : a;
+        }
+        __syncwarp();
+        for (int k = 0; k < m.keep; ++k) {                        // keep the best groups: mark a kept group by +inf
+            float bv = -INFINITY; int bi = 0x7fffffff;
+            for (int g = lane; g < G; g += 32) { const float v = gs[g]; if (v != INFINITY && (v > bv || (v == bv && g < bi))) { bv = v; bi = g; } }
+            warp_argmax(bv, bi);
+            if (lane == 0 && bi < G) gs[bi] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32) if (gs[e / per] != INFINITY) ch[e] = -INFINITY;
+        __syncwarp();
+    }
+    float mine = 0.f; int my_e = 0;      // lane k keeps choice k
+    for (int k = 0; k < m.top; ++k) {
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) { const float v = ch[e]; if (v > bv || (v == bv && e < bi && v != -INFINITY)) { bv = v; bi = e; } }
+        warp_argmax(bv, bi);
+        if (bi >= E) bi = 0;
+        if (lane == k) { my_e = bi; mine = sc[bi]; }
+        if (lane == 0) ch[bi] = -INFINITY;
+        __syncwarp();
+    }
+    float sum = lane < m.top ? mine : 0.f;
+    sum = warp_sum(sum);
+    if (lane < m.top) { idx[(long long)t * m.top + lane] = my_e; wgt[(long long)t * m.top + lane] = mine / (sum + 1e-20f) * m.scale; }
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(256) hy_moe_gate_up_kernel(const TA* h, int ldh, const TA* gu, int ldw, int W, int ff, int ffp, const int32_t* idx, int top, TA* act) {
+    const int row = blockIdx.x, t = row / top, e = idx[row], warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int f = blockIdx.y * 8 + warp;
+    if (f >= ffp) return;
+    float v = 0.f;
+    if (f < ff) {
+        const TA* wg = gu + ((long long)e * 2 * ffp + (f >> 4) * 32 + (f & 15)) * ldw; const TA* wu = wg + 16LL * ldw; const TA* hr = h + (long long)t * ldh;
+        float g = 0.f, u = 0.f;
+        for (int i = lane; i < W; i += 32) { const float x = ldf(hr + i); g = fmaf(x, ldf(wg + i), g); u = fmaf(x, ldf(wu + i), u); }
+        g = warp_sum(g); u = warp_sum(u);
+        v = siluf_(g) * u;
+    }
+    if (lane == 0) stf(act + (long long)row * ffp + f, v);
+}
+template <typename TA>
+__global__ void __launch_bounds__(256) hy_moe_down_kernel(const TA* act, const TA* down, int W, int ffp, const int32_t* idx, const float* wgt, int top, float* x) {
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = blockIdx.y * 8 + warp;
+    if (n >= W) return;
+    float acc = 0.f;
+    for (int c = 0; c < top; ++c) {
+        const int e = idx[(long long)t * top + c];
+        const TA* wd = down + ((long long)e * W + n) * ffp; const TA* ar = act + ((long long)t * top + c) * ffp;
+        float d = 0.f;
+        for (int i = lane; i < ffp; i += 32) d = fmaf(ldf(ar + i), ldf(wd + i), d);
+        d = warp_sum(d);
+        acc = fmaf(wgt[(long long)t * top + c], d, acc);
+    }
+    if (lane == 0) x[(long long)t * W + n] += acc;
+}
+
+// One CTA: counts per expert, 128-row tile table, and each (token, choice)'s destination row — token order inside an expert's tiles, so
+// the plan (and with it every sum) is deterministic.
+__global__ void __launch_bounds__(1024) hy_moe_plan_kernel(const int32_t* idx, int T, int top, int E, int32_t* tile_expert, int32_t* row_src, int32_t* n_tiles_out,
+                                                           int32_t* dst_of, int max_tiles) {
+    extern __shared__ int32_t smi[];
+    int32_t* cnt = smi;           // [E]
+    int32_t* base = smi + E;      // [E] first row of the expert's tiles
+    const int n = T * top;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&cnt[idx[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tiles = 0;
+        for (int e = 0; e < E; ++e) {
+            base[e] = tiles * 128;
+            const int nt = (cnt[e] + 127) / 128;
+            for (int k = 0; k < nt && tiles + k < max_tiles; ++k) tile_expert[tiles + k] = e;
+            tiles += nt;
+        }
+        n_tiles_out[0] = tiles < max_tiles ? tiles : max_tiles;
+    }
+    __syncthreads();
+    const int tiles = n_tiles_out[0];
+    for (int i = threadIdx.x; i < tiles * 128; i += blockDim.x) row_src[i] = -1;
+    __syncthreads();
+    // rank of (token, choice) i inside its expert = number of earlier pairs routed to the same expert; one warp per expert scans in order
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int e = warp; e < E; e += nw) {
+        if (cnt[e] == 0) continue;
+        int run = 0;
+        for (int i0 = 0; i0 < n; i0 += 32) {
+            const int i = i0 + lane; const bool mine = i < n && idx[i] == e;
+            const unsigned bal = __ballot_sync(0xffffffffu, mine);
+            if (mine) { const int dst = base[e] + run + __popc(bal & ((1u << lane) - 1u)); dst_of[i] = dst; row_src[dst] = i; }
+            run += __popc(bal);
+        }
+    }
+}
+__global__ void hy_moe_gather_kernel(const __nv_bfloat16* h, int ldh, int W, const int32_t* row_src, const int32_t* n_tiles, int top, __nv_bfloat16* out) {
+    const int row = blockIdx.x;
+    if (row >= n_tiles[0] * 128) return;
+    const int src = row_src[row];
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    for (int c = threadIdx.x * 8; c < W; c += blockDim.x * 8)
+        *reinterpret_cast<uint4*>(out + (long long)row * W + c) = src >= 0 ? *reinterpret_cast<const uint4*>(h + (long long)(src / top) * ldh + c) : z;
+}
+__global__ void hy_moe_combine_kernel(const float* y, int ldy, const int32_t* dst_of, const float* wgt, int top, float* x, int W) {
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k) acc = fmaf(wgt[(long long)t * top + k], y[(long long)dst_of[(long long)t * top + k] * ldy + c], acc);
+        x[(long long)t * W + c] += acc;
+    }
+}
+
+__global__ void hy_gather_rows_f32_kernel(const float* x, const int32_t* rows, float* out, int W) {
+    const int i = blockIdx.x;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) out[(long long)i * W + c] = x[(long long)rows[i] * W + c];
+}
+__global__ void __launch_bounds__(256) hy_argmax_rows_kernel(const float* logits, int V, int32_t* out_ids) {
+    __shared__ float bv[8]; __shared__ int bi[8];
+    const float* lr = logits + (long long)blockIdx.x * V;
+    float v = -INFINITY; int i = 0x7fffffff;
+    for (int c = threadIdx.x; c < V; c += blockDim.x) { const float f = lr[c]; if (f > v || (f == v && c < i)) { v = f; i = c; } }
+    warp_argmax(v, i);
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = v; bi[threadIdx.x >> 5] = i; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) if (bv[w] > v || (bv[w] == v && bi[w] < i)) { v = bv[w]; i = bi[w]; }
+        out_ids[blockIdx.x] = i < V ? i : 0;
+    }
+}
+__global__ void hy_add_rowvec_kernel(float* x, const float* v, int W) {
+    for (int c = threadIdx.x; c < W; c += blockDim.x) x[(long long)blockIdx.x * W + c] += v[c];
+}
+
+}  // namespace
+
+#define HY_DISPATCH(f32, KERN, ...) ((f32) ? launch_plain(KERN<float>, __VA_ARGS__) : launch_plain(KERN<__nv_bfloat16>, __VA_ARGS__))
+using bf = __nv_bfloat16;
+
+template <typename TA>
+static cudaError_t gemm_t(int mode, const void* A, int lda, const void* B, int ldb, void* C, int ldc, int M, int N, int K, const float* bias, float alpha, int batch,
+                          long long sA, long long sB, long long sC, cudaStream_t s) {
+    dim3 grid((N + 63) / 64, (M + 63) / 64, batch);
+    const TA* a = reinterpret_cast<const TA*>(A); const TA* b = reinterpret_cast<const TA*>(B);
+    switch (mode) {
+        case HY_STORE: return launch_plain(hy_gemm_kernel<TA, HY_STORE>, grid, dim3(256), 0, s, a, lda, b, ldb, C, ldc, M, N, K, bias, alpha, sA, sB, sC);
+        case HY_STORE_F32: return launch_plain(hy_gemm_kernel<TA, HY_STORE_F32>, grid, dim3(256), 0, s, a, lda, b, ldb, C, ldc, M, N, K, bias, alpha, sA, sB, sC);
+        case HY_ACC_F32: return launch_plain(hy_gemm_kernel<TA, HY_ACC_F32>, grid, dim3(256), 0, s, a, lda, b, ldb, C, ldc, M, N, K, bias, alpha, sA, sB, sC);
+    }
+    return cudaErrorInvalidValue;
+}
+cudaError_t hy_gemm(bool f32, int mode, const void* A, int lda, const void* B, int ldb, void* C, int ldc, int M, int N, int K, const float* bias, float alpha, int batch,
+                    long long sA, long long sB, long long sC, cudaStream_t s) {
+    if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return cudaSuccess;
+    return f32 ? gemm_t<float>(mode, A, lda, B, ldb, C, ldc, M, N, K, bias, alpha, batch, sA, sB, sC, s)
+               : gemm_t<bf>(mode, A, lda, B, ldb, C, ldc, M, N, K, bias, alpha, batch, sA, sB, sC, s);
+}
+cudaError_t hy_embed(bool f32, const int32_t* ids, const void* table, float* x, float* x0, int T, int W, int vocab, cudaStream_t s) {
+    return f32 ? launch_plain(hy_embed_kernel<float>, dim3(T), dim3(128), 0, s, ids, (const float*)table, x, x0, T, W, vocab)
+               : launch_plain(hy_embed_kernel<bf>, dim3(T), dim3(128), 0, s, ids, (const bf*)table, x, x0, T, W, vocab);
+}
+cudaError_t hy_concat(bool f32, const float* x, const float* x0, void* cat, int T, int W, cudaStream_t s) {
+    return f32 ? launch_plain(hy_concat_kernel<float>, dim3(T), dim3(128), 0, s, x, x0, (float*)cat, T, W)
+               : launch_plain(hy_concat_kernel<bf>, dim3(T), dim3(128), 0, s, x, x0, (bf*)cat, T, W);
+}
+cudaError_t hy_layernorm(bool f32, const float* x, const int32_t* rows, const float* w, void* out, int ldo, int T, int W, float eps, cudaStream_t s) {
+    if (T <= 0) return cudaSuccess;
+    return f32 ? launch_plain(hy_layernorm_kernel<float>, dim3(T), dim3(256), 0, s, x, rows, w, (float*)out, ldo, W, eps)
+               : launch_plain(hy_layernorm_kernel<bf>, dim3(T), dim3(256), 0, s, x, rows, w, (bf*)out, ldo, W, eps);
+}
+cudaError_t hy_mla_prep(bool f32, const HyLatentAttn& a, const void* q, int ldq, const void* ckv, int ldc, const float* norm_w, float eps, const float* rope_cos,
+                        const float* rope_sin, void* cache, float* q_abs, const HyRows& r, cudaStream_t s) {
+    return f32 ? launch_plain(hy_mla_prep_kernel<float>, dim3(r.T), dim3(128), 0, s, a, (const float*)q, ldq, (const float*)ckv, ldc, norm_w, eps, rope_cos, rope_sin, (float*)cache, q_abs, r)
+               : launch_plain(hy_mla_prep_kernel<bf>, dim3(r.T), dim3(128), 0, s, a, (const bf*)q, ldq, (const bf*)ckv, ldc, norm_w, eps, rope_cos, rope_sin, (bf*)cache, q_abs, r);
+}
+cudaError_t hy_mla_attention(bool f32, const HyLatentAttn& a, const float* q_abs, const void* cache, void* lat_out, const HyRows& r, cudaStream_t s) {
+    if (a.kv_rank > 32 * MLA_ACC) return cudaErrorInvalidValue;
+    const size_t smem = (size_t)(a.kv_rank + a.rot_dim + 4 * a.kv_rank + 8) * 4;
+    return f32 ? launch_plain(hy_mla_attention_kernel<float>, dim3(r.T, a.heads), dim3(128), smem, s, a, q_abs, (const float*)cache, (float*)lat_out, r)
+               : launch_plain(hy_mla_attention_kernel<bf>, dim3(r.T, a.heads), dim3(128), smem, s, a, q_abs, (const bf*)cache, (bf*)lat_out, r);
+}
+cudaError_t hy_conv_silu(bool f32, const void* in, int ld_in, int C, const float* w, const float* bias, int taps, void* out, int ld_out, const void* tails, const HyRows& r,
+                         cudaStream_t s) {
+    dim3 grid((C + 127) / 128, r.T);
+    return f32 ? launch_plain(hy_conv_silu_kernel<float>, grid, dim3(128), 0, s, (const float*)in, ld_in, C, w, bias, taps, (float*)out, ld_out, (const float*)tails, r)
+               : launch_plain(hy_conv_silu_kernel<bf>, grid, dim3(128), 0, s, (const bf*)in, ld_in, C, w, bias, taps, (bf*)out, ld_out, (const bf*)tails, r);
+}
+cudaError_t hy_conv_tails(bool f32, const void* in, int ld_in, int C, int taps, void* tails, const HyRows& r, cudaStream_t s) {
+    if (taps <= 1) return cudaSuccess;
+    dim3 grid((C + 127) / 128, r.S);
+    return f32 ? launch_plain(hy_conv_tails_kernel<float>, grid, dim3(128), 0, s, (const float*)in, ld_in, C, taps, (float*)tails, r)
+               : launch_plain(hy_conv_tails_kernel<bf>, grid, dim3(128), 0, s, (const bf*)in, ld_in, C, taps, (bf*)tails, r);
+}
+cudaError_t hy_delta_prep(bool f32, const HyDelta& d, const void* conv, int ld_conv, const void* b, int ld_b, const void* a, int ld_a, const float* A_log,
+                          const float* dt_bias, float* qq, float* kk, float* vv, float* dec, float* beta, int T, cudaStream_t s) {
+    return f32 ? launch_plain(hy_delta_prep_kernel<float>, dim3(T), dim3(128), 0, s, d, (const float*)conv, ld_conv, (const float*)b, ld_b, (const float*)a, ld_a, A_log, dt_bias, qq, kk, vv, dec, beta)
+               : launch_plain(hy_delta_prep_kernel<bf>, dim3(T), dim3(128), 0, s, d, (const bf*)conv, ld_conv, (const bf*)b, ld_b, (const bf*)a, ld_a, A_log, dt_bias, qq, kk, vv, dec, beta);
+}
+cudaError_t hy_mamba_prep(bool f32, const HyMamba& m, const void* conv, int ld_conv, const void* dt, int ld_dt, const float* A_log, const float* dt_bias, float* qq,
+                          float* kk, float* vv, float* dec, int T, cudaStream_t s) {
+    return f32 ? launch_plain(hy_mamba_prep_kernel<float>, dim3(T), dim3(128), 0, s, m, (const float*)conv, ld_conv, (const float*)dt, ld_dt, A_log, dt_bias, qq, kk, vv, dec)
+               : launch_plain(hy_mamba_prep_kernel<bf>, dim3(T), dim3(128), 0, s, m, (const bf*)conv, ld_conv, (const bf*)dt, ld_dt, A_log, dt_bias, qq, kk, vv, dec);
+}
+cudaError_t hy_recurrence(bool delta, const float* qq, const float* kk, const float* vv, const float* dec, const float* beta, float* out, float* state, int heads,
+                          int qk_heads, int dim, int vdim, const HyRows& r, cudaStream_t s) {
+    const size_t smem = (size_t)(dim * REC_COLS + 3 * dim) * 4;
+    dim3 grid(r.S, heads, (vdim + REC_COLS - 1) / REC_COLS);
+    static bool attr_done[2][16] = {};
+    if (smem > 48 * 1024) {
+        cudaError_t e = delta ? ensure_dynamic_smem(hy_recurrence_kernel<true>, (int)smem, attr_done[0]) : ensure_dynamic_smem(hy_recurrence_kernel<false>, (int)smem, attr_done[1]);
+        if (e != cudaSuccess) return e;
+    }
+    return delta ? launch_plain(hy_recurrence_kernel<true>, grid, dim3(REC_COLS), smem, s, qq, kk, vv, dec, beta, out, state, heads, qk_heads, dim, vdim, r)
+                 : launch_plain(hy_recurrence_kernel<false>, grid, dim3(REC_COLS), smem, s, qq, kk, vv, dec, beta, out, state, heads, qk_heads, dim, vdim, r);
+}
+cudaError_t hy_gated_norm(bool f32, const float* o, int C, int group, const float* w, int wlen, const void* gate, int ld_gate, int gate_before, int act, const float* skip,
+                          int skip_block, const void* xs, int ld_xs, void* out, int ld_out, float eps, int T, cudaStream_t s) {
+    dim3 grid(T, C / group);
+    return f32 ? launch_plain(hy_gated_norm_kernel<float>, grid, dim3(128), 0, s, o, C, group, w, wlen, (const float*)gate, ld_gate, gate_before, act, skip, skip_block, (const float*)xs, ld_xs, (float*)out, ld_out, eps)
+               : launch_plain(hy_gated_norm_kernel<bf>, grid, dim3(128), 0, s, o, C, group, w, wlen, (const bf*)gate, ld_gate, gate_before, act, skip, skip_block, (const bf*)xs, ld_xs, (bf*)out, ld_out, eps);
+}
+cudaError_t hy_moe_router(bool f32, const HyRouter& m, const void* h, int ldh, const void* w_router, int ldw, const float* correction, int W, int32_t* idx, float* wgt,
+                          int T, cudaStream_t s) {
+    const size_t smem = (size_t)(2 * m.experts + m.groups) * 4;
+    return f32 ? launch_plain(hy_moe_router_kernel<float>, dim3(T), dim3(128), smem, s, m, (const float*)h, ldh, (const float*)w_router, ldw, correction, W, idx, wgt)
+               : launch_plain(hy_moe_router_kernel<bf>, dim3(T), dim3(128), smem, s, m, (const bf*)h, ldh, (const bf*)w_router, ldw, correction, W, idx, wgt);
+}
+cudaError_t hy_moe_gate_up(bool f32, const void* h, int ldh, const void* gu, int ldw, int W, int ff, int ffp, const int32_t* idx, int top, void* act, int T, cudaStream_t s) {
+    dim3 grid(T * top, (ffp + 7) / 8);
+    return f32 ? launch_plain(hy_moe_gate_up_kernel<float>, grid, dim3(256), 0, s, (const float*)h, ldh, (const float*)gu, ldw, W, ff, ffp, idx, top, (float*)act)
+               : launch_plain(hy_moe_gate_up_kernel<bf>, grid, dim3(256), 0, s, (const bf*)h, ldh, (const bf*)gu, ldw, W, ff, ffp, idx, top, (bf*)act);
+}
+cudaError_t hy_moe_down(bool f32, const void* act, const void* down, int W, int ffp, const int32_t* idx, const float* wgt, int top, float* x, int T, cudaStream_t s) {
+    dim3 grid(T, (W + 7) / 8);
+    return f32 ? launch_plain(hy_moe_down_kernel<float>, grid, dim3(256), 0, s, (const float*)act, (const float*)down, W, ffp, idx, wgt, top, x)
+               : launch_plain(hy_moe_down_kernel<bf>, grid, dim3(256), 0, s, (const bf*)act, (const bf*)down, W, ffp, idx, wgt, top, x);
+}
+cudaError_t hy_moe_plan(const int32_t* idx, int T, int top, int experts, int32_t* tile_expert, int32_t* row_src, int32_t* n_tiles_out, int32_t* dst_of, int max_tiles,
+                        cudaStream_t s) {
+    return launch_plain(hy_moe_plan_kernel, dim3(1), dim3(1024), (size_t)2 * experts * 4, s, idx, T, top, experts, tile_expert, row_src, n_tiles_out, dst_of, max_tiles);
+}
+cudaError_t hy_moe_gather(const void* h, int ldh, int W, const int32_t* row_src, const int32_t* n_tiles, int top, void* out, int max_tiles, cudaStream_t s) {
+    return launch_plain(hy_moe_gather_kernel, dim3(max_tiles * 128), dim3(128), 0, s, (const bf*)h, ldh, W, row_src, n_tiles, top, (bf*)out);
+}
+cudaError_t hy_moe_combine(const float* y, int ldy, const int32_t* dst_of, const float* wgt, int top, float* x, int W, int T, cudaStream_t s) {
+    return launch_plain(hy_moe_combine_kernel, dim3(T), dim3(256), 0, s, y, ldy, dst_of, wgt, top, x, W);
+}
+cudaError_t hy_gather_rows_f32(const float* x, const int32_t* rows, float* out, int n, int W, cudaStream_t s) {
+    if (n <= 0) return cudaSuccess;
+    return launch_plain(hy_gather_rows_f32_kernel, dim3(n), dim3(128), 0, s, x, rows, out, W);
+}
+cudaError_t hy_argmax_rows(const float* logits, int n, int V, int32_t* out_ids, cudaStream_t s) {
+    if (n <= 0) return cudaSuccess;
+    return launch_plain(hy_argmax_rows_kernel, dim3(n), dim3(256), 0, s, logits, V, out_ids);
+}
+cudaError_t hy_add_rowvec(float* x, const float* v, int T, int W, cudaStream_t s) { return launch_plain(hy_add_rowvec_kernel, dim3(T), dim3(256), 0, s, x, v, W); }
+
+}  // namespace oa

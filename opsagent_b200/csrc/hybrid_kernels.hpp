@@ -1,0 +1,95 @@
+// hybrid_kernels.hpp — launch API of the kernels behind the hybrid decoder family (hybrid_kernels.cu): layer norm, latent attention over a
+// paged latent cache, causal short convolutions with carried tails, the linear recurrences (gated delta rule with per-channel decay, Mamba-2),
+// gated group norms, the grouped-limited sigmoid router and the routed experts.  Each mechanism takes its sizes and constants as arguments.
+//
+// `f32` selects the activation / matrix element type: false = bf16 storage with fp32 accumulation, true = everything in fp32.  What must be
+// fp32 in both modes (residual stream, norms, softmax, router, recurrent state, decays, gates of a recurrence) always is.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace oa {
+
+// per-step row metadata (device pointers into the step's metadata arena).  Rows of one sequence are contiguous.
+struct HyRows {
+    const int32_t* positions;     // [T] position of each row in its sequence
+    const int32_t* slots;         // [T] cache row of each token: page * 64 + offset
+    const int32_t* row_seq;       // [T] sequence index of each row
+    const int32_t* seq_row0;      // [S + 1] first row of each sequence
+    const int32_t* seq_pos0;      // [S] position of a sequence's first row in this step (0: the sequence starts here, its state is taken as zero)
+    const int32_t* seq_state;     // [S] recurrent-state slot
+    const int32_t* block_tables;  // [S, max_pages_per_seq]
+    int max_pages_per_seq, T, S;
+};
+
+enum HyGemmMode : int { HY_STORE = 0, HY_STORE_F32 = 1, HY_ACC_F32 = 2 };
+// C[z][M,N] (op)= alpha * A[z][M,K] . B[z][N,K]^T (+ bias[N]), z < batch with element strides sA/sB/sC.  Plain tiled FMA GEMM in fp32
+// accumulation for any sizes: the fp32 mode's matrix product, and the bf16 mode's fallback where a shape does not fit the tensor-core tiles.
+cudaError_t hy_gemm(bool f32, int mode, const void* A, int lda, const void* B, int ldb, void* C, int ldc, int M, int N, int K, const float* bias,
+                    float alpha, int batch, long long sA, long long sB, long long sC, cudaStream_t s);
+
+cudaError_t hy_embed(bool f32, const int32_t* ids, const void* table, float* x, float* x0, int T, int W, int vocab, cudaStream_t s);
+// cat[t] = [x[t] ; x0[t]] in the activation type (input of the looped block's re-injection projection)
+cudaError_t hy_concat(bool f32, const float* x, const float* x0, void* cat, int T, int W, cudaStream_t s);
+// out[t] = (x[t] - mean) / sqrt(var + eps) * w   (optionally of the rows `rows[i]` only)
+cudaError_t hy_layernorm(bool f32, const float* x, const int32_t* rows, const float* w, void* out, int ldo, int T, int W, float eps, cudaStream_t s);
+
+struct HyLatentAttn {             // sizes of one latent-attention layer
+    int heads, dim, rot_dim, vdim, kv_rank, rot_dims; float scale;
+};
+// From the q projection (q: [T, ldq], head by head [dim | rot_dim]) and the down projection (ckv: [T, ldc] = [kv_rank | rot_dim]):
+// latent = rmsnorm(ckv[:rank]) * norm_w and the rotated shared key go to cache row slots[t] ([rank + rot_dim] per row); the rotated query
+// parts go to q_abs[t, h, rank:] (fp32, [T, heads, rank + rot_dim]).
+cudaError_t hy_mla_prep(bool f32, const HyLatentAttn& a, const void* q, int ldq, const void* ckv, int ldc, const float* norm_w, float eps,
+                        const float* rope_cos, const float* rope_sin, void* cache, float* q_abs, const HyRows& r, cudaStream_t s);
+// causal softmax attention of every row over its sequence's cached rows 0..position, with absorbed queries q_abs = [W_uk^T q_unrotated | q_rotated]:
+// lat_out[t, h, :rank] = sum_j softmax_j(scale * q_abs[t,h] . cache[j]) cache[j][:rank]
+cudaError_t hy_mla_attention(bool f32, const HyLatentAttn& a, const float* q_abs, const void* cache, void* lat_out, const HyRows& r, cudaStream_t s);
+
+// y = silu(causal conv over time of `in` per channel (+ bias)); inputs before a sequence's first row of this step come from its tail
+// (the last taps-1 inputs of earlier steps; zeros at the start of a sequence).  hy_conv_tails then stores the new tails.
+cudaError_t hy_conv_silu(bool f32, const void* in, int ld_in, int C, const float* w, const float* bias, int taps, void* out, int ld_out,
+                         const void* tails, const HyRows& r, cudaStream_t s);
+cudaError_t hy_conv_tails(bool f32, const void* in, int ld_in, int C, int taps, void* tails, const HyRows& r, cudaStream_t s);
+
+struct HyDelta { int heads, kv_heads, dim, vdim; };
+// unit-norm q (times dim^-1/2) and k, v, beta = sigmoid(b), per-channel decay exp(-exp(A_log_h) softplus(a + dt_bias)) — all fp32
+cudaError_t hy_delta_prep(bool f32, const HyDelta& d, const void* qkv_conv, int ld_conv, const void* b, int ld_b, const void* a, int ld_a,
+                          const float* A_log, const float* dt_bias, float* qq, float* kk, float* vv, float* dec, float* beta, int T, cudaStream_t s);
+struct HyMamba { int heads, vdim, state, groups; };
+// dt = softplus(dt + dt_bias); decay exp(-exp(A_log_h) dt); kk = B, qq = C, vv = dt * x — all fp32
+cudaError_t hy_mamba_prep(bool f32, const HyMamba& m, const void* xbc_conv, int ld_conv, const void* dt, int ld_dt, const float* A_log,
+                          const float* dt_bias, float* qq, float* kk, float* vv, float* dec, int T, cudaStream_t s);
+// The linear recurrence both mixers share, per (sequence, head) on an fp32 state S[dim, vdim] carried in `state` (slot-major):
+//   delta:  S <- diag(dec_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
+//   plain:  S <- dec_t S + k_t v_t^T;                                            o_t = S^T q_t
+// qq/kk: [T, qk_heads, dim]; vv/out: [T, heads, vdim]; dec: [T, heads, dim] (delta) or [T, heads]; head h reads q/k head h / (heads / qk_heads)
+cudaError_t hy_recurrence(bool delta, const float* qq, const float* kk, const float* vv, const float* dec, const float* beta, float* out,
+                          float* state, int heads, int qk_heads, int dim, int vdim, const HyRows& r, cudaStream_t s);
+// group-wise RMS norm with a gate: v = o (+ skip[c / skip_block] * xs[t, c]); gate_before ? v *= act(gate) : -; v /= rms over each group of
+// `group` channels; v *= w[c % wlen]; !gate_before ? v *= act(gate) : -.  act: 0 = sigmoid, 1 = silu.
+cudaError_t hy_gated_norm(bool f32, const float* o, int C, int group, const float* w, int wlen, const void* gate, int ld_gate, int gate_before, int act,
+                          const float* skip, int skip_block, const void* xs, int ld_xs, void* out, int ld_out, float eps, int T, cudaStream_t s);
+
+struct HyRouter { int experts, top, groups, keep; float scale; };
+// sigmoid router with a selection-only correction and group-limited choice: idx[t, top], wgt[t, top] (weights = chosen sigmoids / their sum * scale)
+cudaError_t hy_moe_router(bool f32, const HyRouter& m, const void* h, int ldh, const void* w_router, int ldw, const float* correction, int W,
+                          int32_t* idx, float* wgt, int T, cudaStream_t s);
+// routed experts, one (token, choice) at a time (decode-sized batches and the fp32 mode).  gu: [E][2 ffp][ldw] with gate / up rows interleaved in
+// blocks of 16, down: [E][W][ffp]; act: [T * top, ffp]
+cudaError_t hy_moe_gate_up(bool f32, const void* h, int ldh, const void* gu, int ldw, int W, int ff, int ffp, const int32_t* idx, int top, void* act, int T, cudaStream_t s);
+cudaError_t hy_moe_down(bool f32, const void* act, const void* down, int W, int ffp, const int32_t* idx, const float* wgt, int top, float* x, int T, cudaStream_t s);
+
+// grouped (tensor-core) expert path: rows sorted by expert into 128-row tiles
+// counts -> tile table: tile_expert[n_tiles], row_src[n_tiles * 128] (token * top + choice, or -1), n_tiles_out[1]
+cudaError_t hy_moe_plan(const int32_t* idx, int T, int top, int experts, int32_t* tile_expert, int32_t* row_src, int32_t* n_tiles_out, int32_t* dst_of, int max_tiles, cudaStream_t s);
+cudaError_t hy_moe_gather(const void* h, int ldh, int W, const int32_t* row_src, const int32_t* n_tiles, int top, void* out, int max_tiles, cudaStream_t s);
+// x[t] += sum over choices (in order) wgt[t,c] * y[dst_of[t*top+c]]
+cudaError_t hy_moe_combine(const float* y, int ldy, const int32_t* dst_of, const float* wgt, int top, float* x, int W, int T, cudaStream_t s);
+
+cudaError_t hy_gather_rows_f32(const float* x, const int32_t* rows, float* out, int n, int W, cudaStream_t s);
+cudaError_t hy_argmax_rows(const float* logits, int n, int V, int32_t* out_ids, cudaStream_t s);
+// x[t, :] += v[:]
+cudaError_t hy_add_rowvec(float* x, const float* v, int T, int W, cudaStream_t s);
+
+}  // namespace oa

@@ -1,0 +1,397 @@
+// hybrid_model.cpp — see hybrid_model.hpp.
+#include "hybrid_model.hpp"
+
+#include <sys/stat.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <stdexcept>
+
+#include "common.cuh"
+#include "safetensors.hpp"
+
+namespace oa {
+
+struct HybridModel::SafeTensorsHolder { SafeTensors st; explicit SafeTensorsHolder(const std::string& p) : st(p) {} };
+
+static int up8(int n) { return (n + 7) & ~7; }
+static int up16(int n) { return (n + 15) & ~15; }
+
+struct HyDeviceGuard {
+    int prev = -1;
+    explicit HyDeviceGuard(int dev) { cudaGetDevice(&prev); cudaSetDevice(dev); }
+    ~HyDeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+void* HybridModel::dmalloc(size_t bytes) {
+    void* p = nullptr;
+    cuda_check(cudaMalloc(&p, bytes ? bytes : 16), "cudaMalloc");
+    cuda_check(cudaMemset(p, 0, bytes ? bytes : 16), "cudaMemset");
+    allocs_.push_back(p);
+    return p;
+}
+float* HybridModel::upload_f32(const std::vector<float>& v) {
+    float* d = reinterpret_cast<float*>(dmalloc(v.size() * 4));
+    cuda_check(cudaMemcpy(d, v.data(), v.size() * 4, cudaMemcpyHostToDevice), "H2D");
+    return d;
+}
+void* HybridModel::upload_act(const std::vector<float>& v) {
+    weight_bytes += v.size() * es_;
+    if (f32_) return upload_f32(v);
+    std::vector<uint16_t> b(v.size());
+    for (size_t i = 0; i < v.size(); ++i) b[i] = f32_to_bf16_bits(v[i]);
+    void* d = dmalloc(b.size() * 2);
+    cuda_check(cudaMemcpy(d, b.data(), b.size() * 2, cudaMemcpyHostToDevice), "H2D");
+    return d;
+}
+HybridModel::Mat HybridModel::upload_mat(const HostMat& m) {
+    Mat d; d.N = m.N; d.K = m.K; d.ld = up8(m.K);
+    std::vector<float> padded((size_t)up8(m.N) * d.ld, 0.f);          // rows padded too: a tensor-core tile may read past N
+    for (int r = 0; r < m.N; ++r) std::memcpy(&padded[(size_t)r * d.ld], &m.v[(size_t)r * m.K], (size_t)m.K * 4);
+    d.p = upload_act(padded);
+    if (!f32_ && opt.hy_tensor_core) {
+        const int bns[4] = {32, 64, 128, 256}; d.tc = true;
+        for (int i = 0; i < 4; ++i)
+            if (make_tmap_bf16_2d(&d.tm[i], d.p, (uint64_t)up8(m.N), (uint64_t)d.ld, (uint64_t)d.ld, (uint32_t)bns[i], 64) != 0) d.tc = false;
+    }
+    return d;
+}
+
+static uint64_t name_hash(const std::string& s, uint64_t seed) {
+    uint64_t h = 0xcbf29ce484222325ull ^ seed;
+    for (unsigned char c : s) { h ^= c; h *= 0x100000001b3ull; }
+    return h;
+}
+static float unit_rand(uint64_t& st) {        // uniform in [-1, 1)
+    st += 0x9E3779B97F4A7C15ull; uint64_t z = st; z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull; z = (z ^ (z >> 27)) * 0x94D049BB133111EBull; z ^= z >> 31;
+    return (float)((double)(z >> 11) * (1.0 / 9007199254740992.0) * 2.0 - 1.0);
+}
+static float bf16_round(float f) { const uint32_t u = (uint32_t)f32_to_bf16_bits(f) << 16; float o; std::memcpy(&o, &u, 4); return o; }
+
+static void st_to_f32(const StTensor& t, std::vector<float>& out) {
+    size_t n = 1; for (int64_t d : t.shape) n *= (size_t)d;
+    out.resize(n);
+    if (t.dtype == "BF16") { const uint16_t* s = reinterpret_cast<const uint16_t*>(t.data); for (size_t i = 0; i < n; ++i) { const uint32_t u = (uint32_t)s[i] << 16; std::memcpy(&out[i], &u, 4); } }
+    else if (t.dtype == "F32") std::memcpy(out.data(), t.data, n * 4);
+    else throw std::runtime_error("checkpoint dtype " + t.dtype + " is not supported for this model family (BF16 or F32)");
+}
+
+HybridModel::HostMat HybridModel::tensor(const std::string& name, int N, int K) {
+    HostMat m; m.N = N; m.K = K;
+    if (st_) {
+        const StTensor& t = st_->st.get(name);
+        const bool ok = t.shape.size() == 2 && t.shape[0] == N && (K == 0 || t.shape[1] == K);
+        if (!ok) throw std::runtime_error("checkpoint tensor " + name + " does not have the shape the configuration implies");
+        m.K = (int)t.shape[1];
+        st_to_f32(t, m.v);
+    } else {
+        if (K == 0) m.K = K = std::max(8, hc_.width / 16);     // low-rank width of a seeded model
+        uint64_t s = name_hash(name, cfg.seed);
+        const float a = std::sqrt(3.0f / (float)K);
+        m.v.resize((size_t)N * K);
+        for (auto& x : m.v) x = bf16_round(a * unit_rand(s));
+    }
+    return m;
+}
+std::vector<float> HybridModel::vec(const std::string& name, int n, float init_mean, float init_spread) {
+    std::vector<float> v;
+    if (st_) {
+        const StTensor& t = st_->st.get(name);
+        size_t have = 1; for (int64_t d : t.shape) have *= (size_t)d;
+        if ((int)have != n) throw std::runtime_error("checkpoint tensor " + name + " does not have the size the configuration implies");
+        st_to_f32(t, v);
+    } else {
+        uint64_t s = name_hash(name, cfg.seed); v.resize(n);
+        for (auto& x : v) x = bf16_round(init_mean + init_spread * unit_rand(s));
+    }
+    return v;
+}
+static void append_rows(std::vector<float>& dst, int& rows, int K, const std::vector<float>& src, int src_rows, int align) {
+    while (rows % align) { dst.resize(dst.size() + K, 0.f); ++rows; }
+    dst.insert(dst.end(), src.begin(), src.end()); rows += src_rows;
+}
+
+HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBase(c, o), hc_(*c.hybrid) {
+    HyDeviceGuard guard(opt.device);
+    cuda_check(cudaSetDevice(opt.device), "cudaSetDevice");
+    cudaDeviceProp prop;
+    cuda_check(cudaGetDeviceProperties(&prop, opt.device), "cudaGetDeviceProperties");
+    if (prop.major != 10) throw std::runtime_error("opsagent_b200 requires an sm_100 (Blackwell B200) device");
+    if (opt.tp != 1) throw std::runtime_error("the hybrid model family runs on one GPU per engine (tp = 1)");
+    sm_count = prop.multiProcessorCount;
+    cuda_check(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "cudaStreamCreate");
+    f32_ = opt.f32 != 0; es_ = f32_ ? 4 : 2;
+    const int W = hc_.width, V = hc_.vocab; Wld_ = up8(W);
+    {
+        struct stat sb; const std::string f = hc_.dir + "/model.safetensors";
+        if (stat(f.c_str(), &sb) == 0) st_ = new SafeTensorsHolder(f);
+    }
+    // ---- weights ----
+    embed_ = upload_act(tensor("embed", V, W).v);
+    head_ = upload_mat(tensor("head", V, W));
+    final_norm_ = upload_f32(vec("final.norm", W, 1.f, 0.1f));
+    if (hc_.loop_times > 0) { loop_in_ = upload_mat(tensor("loop.in", W, 2 * W)); loop_step_ = upload_f32(vec("loop.step", hc_.loop_times * W, 0.f, 0.1f)); }
+    lw_.resize(hc_.layers.size());
+    int max_in = 8, max_p2 = 8, max_conv = 8, max_mix = 8, max_qabs = 8, max_lat = 8, max_qk = 8, max_v = 8, max_dec = 8, max_h = 8, max_act = 8, max_top = 1, max_E = 1;
+    for (size_t li = 0; li < hc_.layers.size(); ++li) {
+        const HyLayer& l = hc_.layers[li]; LayerW& w = lw_[li];
+        const std::string p = "l" + std::to_string(li) + ".", mx = p + "mix.";
+        w.norm1 = upload_f32(vec(p + "norm1", W, 1.f, 0.1f));
+        HostMat in; in.K = W; int rows = 0;
+        if (l.type == HY_LATENT_ATTENTION) {
+            const int qd = l.heads * (l.dim + l.rot_dim), E = l.kv_rank + l.rot_dim;
+            append_rows(in.v, rows, W, tensor(mx + "q", qd, W).v, qd, 1); w.off_a = 0;
+            while (rows % 8) { in.v.resize(in.v.size() + W, 0.f); ++rows; }
+            w.off_b = rows; append_rows(in.v, rows, W, tensor(mx + "dkv", E, W).v, E, 1);
+            w.dkv_norm = upload_f32(vec(mx + "dkv.norm", l.kv_rank, 1.f, 0.1f));
+            // W_uk per head transposed to [rank, dim]: the absorbed query W_uk^T q is then an ordinary A . B^T product
+            HostMat uk = tensor(mx + "uk", l.heads * l.dim, l.kv_rank);
+            std::vector<float> ukt((size_t)l.heads * l.kv_rank * l.dim);
+            for (int h = 0; h < l.heads; ++h) for (int d = 0; d < l.dim; ++d) for (int r = 0; r < l.kv_rank; ++r)
+                ukt[((size_t)h * l.kv_rank + r) * l.dim + d] = uk.v[((size_t)h * l.dim + d) * l.kv_rank + r];
+            w.uk_t = upload_act(ukt);
+            w.uv = upload_act(tensor(mx + "uv", l.heads * l.vdim, l.kv_rank).v);
+            w.o = upload_mat(tensor(mx + "o", W, l.heads * l.vdim));
+            for (size_t i = 0; i < ropes_.size(); ++i) if (ropes_[i].base == l.rot_base && ropes_[i].dims == l.rot_dims) w.rope = (int)i;
+            if (w.rope < 0) {
+                RopeTable rt; rt.base = l.rot_base; rt.dims = l.rot_dims; const int half = l.rot_dims / 2;
+                std::vector<float> cs((size_t)opt.max_seq_len * std::max(1, half)), sn(cs.size());
+                for (int i = 0; i < half; ++i) {
+                    const double f = std::pow((double)l.rot_base, -2.0 * i / (double)l.rot_dims);
+                    for (int ps = 0; ps < opt.max_seq_len; ++ps) { cs[(size_t)ps * half + i] = (float)std::cos(ps * f); sn[(size_t)ps * half + i] = (float)std::sin(ps * f); }
+                }
+                rt.cos = upload_f32(cs); rt.sin = upload_f32(sn); w.rope = (int)ropes_.size(); ropes_.push_back(rt);
+            }
+            max_qabs = std::max(max_qabs, l.heads * E); max_lat = std::max(max_lat, l.heads * l.kv_rank); max_mix = std::max(max_mix, l.heads * l.vdim);
+        } else if (l.type == HY_CHANNEL_DELTA) {
+            const int qk = l.kv_heads * l.dim, vd = l.heads * l.vdim;
+            append_rows(in.v, rows, W, tensor(mx + "q", qk, W).v, qk, 1); append_rows(in.v, rows, W, tensor(mx + "k", qk, W).v, qk, 1);
+            append_rows(in.v, rows, W, tensor(mx + "v", vd, W).v, vd, 1);
+            w.off_a = 0; w.conv_ch = 2 * qk + vd;
+            while (rows % 8) { in.v.resize(in.v.size() + W, 0.f); ++rows; }
+            w.off_b = rows; append_rows(in.v, rows, W, tensor(mx + "b", l.heads, W).v, l.heads, 1);
+            while (rows % 8) { in.v.resize(in.v.size() + W, 0.f); ++rows; }
+            HostMat a1 = tensor(mx + "a1", st_ ? (int)st_->st.get(mx + "a1").shape[0] : std::max(8, W / 16), W);
+            w.off_c = rows; w.a_rank = a1.N; append_rows(in.v, rows, W, a1.v, a1.N, 1);
+            while (rows % 8) { in.v.resize(in.v.size() + W, 0.f); ++rows; }
+            HostMat g1 = tensor(mx + "g1", st_ ? (int)st_->st.get(mx + "g1").shape[0] : std::max(8, W / 16), W);
+            w.off_d = rows; w.g_rank = g1.N; append_rows(in.v, rows, W, g1.v, g1.N, 1);
+            w.a2 = upload_mat(tensor(mx + "a2", l.heads * l.dim, w.a_rank)); w.g2 = upload_mat(tensor(mx + "g2", vd, w.g_rank));
+            w.A_log = upload_f32(vec(mx + "A_log", l.heads, 0.f, 0.5f)); w.dt_bias = upload_f32(vec(mx + "dt_bias", l.heads * l.dim, 0.f, 0.5f));
+            w.norm_w = upload_f32(vec(mx + "norm", l.vdim, 1.f, 0.1f));
+            std::vector<float> cw = vec(mx + "q.conv", qk * l.conv, 0.f, 0.5f), ck = vec(mx + "k.conv", qk * l.conv, 0.f, 0.5f), cv = vec(mx + "v.conv", vd * l.conv, 0.f, 0.5f);
+            cw.insert(cw.end(), ck.begin(), ck.end()); cw.insert(cw.end(), cv.begin(), cv.end());
+            w.conv_w = upload_f32(cw);
+            w.o = upload_mat(tensor(mx + "o", W, vd));
+            max_p2 = std::max(max_p2, up8(l.heads * l.dim) + vd); max_conv = std::max(max_conv, w.conv_ch); max_mix = std::max(max_mix, vd);
+            max_qk = std::max(max_qk, qk); max_v = std::max(max_v, vd); max_dec = std::max(max_dec, l.heads * l.dim); max_h = std::max(max_h, l.heads);
+        } else {
+            const int inner = l.heads * l.vdim, gn = l.groups * l.state, n_in = 2 * inner + 2 * gn + l.heads;
+            append_rows(in.v, rows, W, tensor(mx + "in", n_in, W).v, n_in, 1);
+            w.off_a = 0; w.off_b = inner; w.off_c = 2 * inner + 2 * gn; w.conv_ch = inner + 2 * gn;
+            w.conv_w = upload_f32(vec(mx + "conv", w.conv_ch * l.conv, 0.f, 0.5f)); w.conv_b = upload_f32(vec(mx + "conv.b", w.conv_ch, 0.f, 0.1f));
+            w.dt_bias = upload_f32(vec(mx + "dt_bias", l.heads, 0.f, 0.5f)); w.A_log = upload_f32(vec(mx + "A_log", l.heads, 0.f, 0.5f));
+            w.D = upload_f32(vec(mx + "D", l.heads, 1.f, 0.2f)); w.norm_w = upload_f32(vec(mx + "norm", inner, 1.f, 0.1f));
+            w.o = upload_mat(tensor(mx + "o", W, inner));
+            max_conv = std::max(max_conv, w.conv_ch); max_mix = std::max(max_mix, inner); max_qk = std::max(max_qk, gn); max_v = std::max(max_v, inner);
+            max_dec = std::max(max_dec, l.heads); max_h = std::max(max_h, l.heads);
+        }
+        in.N = rows; w.in = upload_mat(in);
+        max_in = std::max(max_in, up8(rows));
+        if (l.moe.present) {
+            const HyMoe& m = l.moe; const std::string mp = p + "mlp.";
+            w.router = upload_mat(tensor(mp + "router", m.experts, W));
+            w.correction = upload_f32(vec(mp + "correction", m.experts, 0.f, 0.05f));
+            w.ffp = up16(m.ff);
+            std::vector<float> gu((size_t)m.experts * 2 * w.ffp * Wld_, 0.f), dn((size_t)m.experts * W * w.ffp, 0.f);
+            for (int e = 0; e < m.experts; ++e) {
+                const std::string ep = mp + "e" + std::to_string(e) + ".";
+                HostMat g = tensor(ep + "gate", m.ff, W), u = tensor(ep + "up", m.ff, W), d = tensor(ep + "down", W, m.ff);
+                for (int f = 0; f < m.ff; ++f) {
+                    const size_t pg = ((size_t)e * 2 * w.ffp + (size_t)(f >> 4) * 32 + (f & 15)) * Wld_;
+                    std::memcpy(&gu[pg], &g.v[(size_t)f * W], (size_t)W * 4); std::memcpy(&gu[pg + (size_t)16 * Wld_], &u.v[(size_t)f * W], (size_t)W * 4);
+                }
+                for (int n = 0; n < W; ++n) std::memcpy(&dn[((size_t)e * W + n) * w.ffp], &d.v[(size_t)n * m.ff], (size_t)m.ff * 4);
+            }
+            w.gu = upload_act(gu); w.down = upload_act(dn);
+            max_act = std::max(max_act, m.top * w.ffp); max_top = std::max(max_top, m.top); max_E = std::max(max_E, m.experts);
+        }
+    }
+    delete st_; st_ = nullptr;
+
+    // ---- activations ----
+    MR_ = std::max(opt.max_step_tokens, opt.max_batch); MS_ = std::max(opt.max_batch, std::min(MR_, 4096));
+    const size_t MR = (size_t)MR_;
+    x_ = (float*)dmalloc(MR * W * 4); x0_ = (float*)dmalloc(MR * W * 4);
+    cat_ = dmalloc(MR * 2 * Wld_ * es_); h_ = dmalloc(MR * Wld_ * es_);
+    ld_proj_ = max_in; ld_p2_ = up8(max_p2); ld_conv_ = up8(max_conv); ld_mix_ = up8(max_mix);
+    proj_ = dmalloc(MR * ld_proj_ * es_); p2_ = dmalloc(MR * ld_p2_ * es_); conv_ = dmalloc(MR * ld_conv_ * es_); mix_ = dmalloc(MR * ld_mix_ * es_);
+    q_abs_ = (float*)dmalloc(MR * max_qabs * 4); lat_ = dmalloc(MR * up8(max_lat) * es_);
+    qq_ = (float*)dmalloc(MR * max_qk * 4); kk_ = (float*)dmalloc(MR * max_qk * 4); vv_ = (float*)dmalloc(MR * max_v * 4); rec_ = (float*)dmalloc(MR * max_v * 4);
+    dec_ = (float*)dmalloc(MR * max_dec * 4); beta_ = (float*)dmalloc(MR * max_h * 4);
+    idx_ = (int32_t*)dmalloc(MR * max_top * 4); wgt_ = (float*)dmalloc(MR * max_top * 4); act_ = dmalloc(MR * max_act * es_);
+    hs_ = dmalloc((size_t)MS_ * Wld_ * es_); logits_ = (float*)dmalloc((size_t)MS_ * V * 4); d_out_ids_ = (int32_t*)dmalloc((size_t)MS_ * 4);
+    cuda_check(cudaMallocHost(&h_out_ids, (size_t)MS_ * 4), "cudaMallocHost");
+    mask_words = (V + 31) / 32; mask_slots = 0; max_mask_updates = 0;       // grammar-constrained sampling is not wired to this family's head
+
+    // ---- paged latent cache + state slots ----
+    size_t page_bytes = 0;
+    for (const HyRun& r : hc_.runs) if (r.cache_idx >= 0) { const HyLayer& l = hc_.layers[r.layer]; page_bytes += (size_t)64 * (l.kv_rank + l.rot_dim) * es_; }
+    if (opt.num_pages > 0) num_pages = opt.num_pages;
+    else {
+        size_t free_b = 0, total_b = 0;
+        cuda_check(cudaMemGetInfo(&free_b, &total_b), "cudaMemGetInfo");
+        double budget = opt.kv_gb > 0 ? opt.kv_gb * 1e9 : (double)free_b - 6e9;
+        budget = std::min(budget, (double)free_b - 2e9);
+        num_pages = (int)std::max(0.0, std::min(budget / (double)std::max<size_t>(page_bytes, 1), 4.0e6));
+    }
+    max_pages_per_seq = opt.max_seq_len / 64;
+    if (num_pages < 1) throw std::runtime_error("cache pool too small");
+    caches_.resize(hc_.n_caches); states_.resize(hc_.n_states); tails_.resize(hc_.n_states);
+    state_slots = hc_.n_states > 0 ? opt.max_batch : 0;
+    for (const HyRun& r : hc_.runs) {
+        const HyLayer& l = hc_.layers[r.layer];
+        if (r.cache_idx >= 0) { const size_t b = (size_t)num_pages * 64 * (l.kv_rank + l.rot_dim) * es_; caches_[r.cache_idx] = dmalloc(b); kv_pool_bytes += b; }
+        else {
+            const int sd = l.type == HY_CHANNEL_DELTA ? l.dim : l.state;
+            states_[r.state_idx] = (float*)dmalloc((size_t)state_slots * l.heads * sd * l.vdim * 4);
+            tails_[r.state_idx] = dmalloc((size_t)state_slots * std::max(1, l.conv - 1) * lw_[r.layer].conv_ch * es_);
+        }
+    }
+    meta_cap_words_ = 4 * MR + (size_t)MS_ + (size_t)opt.max_batch * (max_pages_per_seq + 8) + 64;
+    for (int i = 0; i < 2; ++i) {
+        cuda_check(cudaMallocHost(&h_meta_buf_[i], meta_cap_words_ * 4), "cudaMallocHost meta");
+        cuda_check(cudaEventCreateWithFlags(&meta_ev_[i], cudaEventDisableTiming), "cudaEventCreate meta");
+    }
+    d_meta_ = (int32_t*)dmalloc(meta_cap_words_ * 4);
+    (void)max_E;
+    cuda_check(cudaStreamSynchronize(stream), "init sync");
+}
+
+HybridModel::~HybridModel() {
+    HyDeviceGuard guard(opt.device);
+    if (stream) cudaStreamSynchronize(stream);
+    for (void* p : allocs_) cudaFree(p);
+    if (h_out_ids) cudaFreeHost(h_out_ids);
+    for (int i = 0; i < 2; ++i) { if (h_meta_buf_[i]) cudaFreeHost(h_meta_buf_[i]); if (meta_ev_[i]) cudaEventDestroy(meta_ev_[i]); }
+    if (stream) cudaStreamDestroy(stream);
+    delete st_;
+}
+
+void HybridModel::gemm(int mode, const void* A, int lda, const Mat& B, void* C, int ldc, int M, const float* bias, float alpha) {
+    cuda_check(hy_gemm(f32_, mode, A, lda, B.p, B.ld, C, ldc, M, B.N, B.K, bias, alpha, 1, 0, 0, 0, stream), "gemm");
+}
+
+void HybridModel::moe(const LayerW& w, const HyLayer& l, const HyRows& r) {
+    const HyMoe& m = l.moe; const int W = hc_.width, T = r.T;
+    HyRouter hr{m.experts, m.top, m.groups, m.keep, m.scale};
+    cuda_check(hy_moe_router(f32_, hr, h_, Wld_, w.router.p, w.router.ld, w.correction, W, idx_, wgt_, T, stream), "router");
+    cuda_check(hy_moe_gate_up(f32_, h_, Wld_, w.gu, Wld_, W, m.ff, w.ffp, idx_, m.top, act_, T, stream), "experts gate/up");
+    cuda_check(hy_moe_down(f32_, act_, w.down, W, w.ffp, idx_, wgt_, m.top, x_, T, stream), "experts down");
+}
+
+void HybridModel::forward(const StepInput& in, float* logits_out) {
+    const int T = (int)in.tokens.size(), S = in.n_seqs, NS = (int)in.sample_rows.size(), W = hc_.width, V = hc_.vocab;
+    if (T <= 0 || T > MR_ || NS > MS_ || S <= 0 || S > opt.max_batch) throw std::runtime_error("forward: bad batch size");
+    if ((int)in.seq_row0.size() != S + 1 || (int)in.state_slots.size() != S || in.seq_row0[S] != T) throw std::runtime_error("forward: this model needs the rows of every sequence (seq_row0) and its state slot");
+    row_seq_.resize(T); seq_pos0_.resize(S);
+    for (int s = 0; s < S; ++s) {
+        if (in.seq_row0[s + 1] <= in.seq_row0[s]) throw std::runtime_error("forward: empty sequence in a step");
+        if (state_slots > 0 && (in.state_slots[s] < 0 || in.state_slots[s] >= state_slots)) throw std::runtime_error("forward: state slot out of range");
+        seq_pos0_[s] = in.positions[in.seq_row0[s]];
+        for (int t = in.seq_row0[s]; t < in.seq_row0[s + 1]; ++t) { row_seq_[t] = s; if (in.positions[t] != seq_pos0_[s] + (t - in.seq_row0[s])) throw std::runtime_error("forward: rows of a sequence must be consecutive positions"); }
+        if (in.positions[in.seq_row0[s + 1] - 1] >= opt.max_seq_len) throw std::runtime_error("forward: position beyond max_seq_len");
+    }
+    meta_idx_ ^= 1; int32_t* hm = h_meta_buf_[meta_idx_];
+    cuda_check(cudaEventSynchronize(meta_ev_[meta_idx_]), "meta staging fence");
+    size_t wd = 0;
+    auto put = [&](const void* src, size_t words) -> size_t {
+        size_t at = wd; if (at + words > meta_cap_words_) throw std::runtime_error("forward: metadata arena overflow");
+        if (words) std::memcpy(hm + at, src, words * 4);
+        wd = (at + words + 3) & ~size_t(3); return at;
+    };
+    const size_t o_tok = put(in.tokens.data(), T), o_pos = put(in.positions.data(), T), o_slot = put(in.slots.data(), T), o_samp = put(in.sample_rows.data(), NS);
+    const size_t o_bt = put(in.block_tables.data(), in.block_tables.size()), o_rs = put(row_seq_.data(), T), o_r0 = put(in.seq_row0.data(), S + 1);
+    const size_t o_p0 = put(seq_pos0_.data(), S), o_st = put(in.state_slots.data(), S);
+    cuda_check(cudaMemcpyAsync(d_meta_, hm, wd * 4, cudaMemcpyHostToDevice, stream), "meta H2D");
+    cuda_check(cudaEventRecord(meta_ev_[meta_idx_], stream), "meta event");
+    h2d_bytes += wd * 4;
+    HyRows r{d_meta_ + o_pos, d_meta_ + o_slot, d_meta_ + o_rs, d_meta_ + o_r0, d_meta_ + o_p0, d_meta_ + o_st, d_meta_ + o_bt, max_pages_per_seq, T, S};
+    static const char* dbg_layers = std::getenv("OA_DEBUG_LAYERS");      // debug: file that receives the residual stream after every layer execution of each forward
+    std::vector<float> dbg_buf;
+    if (dbg_layers && !capture_layers) capture_layers = &dbg_buf;
+    if (capture_layers) capture_layers->clear();
+
+    cuda_check(hy_embed(f32_, d_meta_ + o_tok, embed_, x_, x0_, T, W, V, stream), "embed");
+    auto at = [&](void* base, size_t elems) -> void* { return reinterpret_cast<char*>(base) + elems * es_; };
+    for (const HyRun& run : hc_.runs) {
+        const HyLayer& l = hc_.layers[run.layer]; const LayerW& w = lw_[run.layer];
+        if (run.first_of_pass) {         // re-injection: x <- W_in [x ; x0] + step[pass]
+            cuda_check(hy_concat(f32_, x_, x0_, cat_, T, W, stream), "concat");
+            gemm(HY_STORE_F32, cat_, 2 * W, loop_in_, x_, W, T, loop_step_ + (size_t)run.pass * W, 1.f);
+        }
+        cuda_check(hy_layernorm(f32_, x_, nullptr, w.norm1, h_, Wld_, T, W, hc_.eps, stream), "layer norm");
+        gemm(HY_STORE, h_, Wld_, w.in, proj_, ld_proj_, T, nullptr, 1.f);
+        if (l.type == HY_LATENT_ATTENTION) {
+            const HyLatentAttn a{l.heads, l.dim, l.rot_dim, l.vdim, l.kv_rank, l.rot_dims, l.scale};
+            const int E = l.kv_rank + l.rot_dim;
+            // absorbed queries: q_abs[t, h, :rank] = W_uk[h]^T q_unrotated[t, h]
+            cuda_check(hy_gemm(f32_, HY_STORE_F32, at(proj_, w.off_a), ld_proj_, w.uk_t, l.dim, q_abs_, l.heads * E, T, l.kv_rank, l.dim, nullptr, 1.f, l.heads,
+                               l.dim + l.rot_dim, (long long)l.kv_rank * l.dim, E, stream), "query absorption");
+            cuda_check(hy_mla_prep(f32_, a, at(proj_, w.off_a), ld_proj_, at(proj_, w.off_b), ld_proj_, w.dkv_norm, hc_.eps, ropes_[w.rope].cos, ropes_[w.rope].sin,
+                                   caches_[run.cache_idx], q_abs_, r, stream), "latent cache write");
+            cuda_check(hy_mla_attention(f32_, a, q_abs_, caches_[run.cache_idx], lat_, r, stream), "latent attention");
+            cuda_check(hy_gemm(f32_, HY_STORE, lat_, l.heads * l.kv_rank, w.uv, l.kv_rank, mix_, ld_mix_, T, l.vdim, l.kv_rank, nullptr, 1.f, l.heads, l.kv_rank,
+                               (long long)l.vdim * l.kv_rank, l.vdim, stream), "value up-projection");
+        } else if (l.type == HY_CHANNEL_DELTA) {
+            const HyDelta d{l.heads, l.kv_heads, l.dim, l.vdim};
+            cuda_check(hy_conv_silu(f32_, at(proj_, w.off_a), ld_proj_, w.conv_ch, w.conv_w, nullptr, l.conv, conv_, ld_conv_, tails_[run.state_idx], r, stream), "conv");
+            cuda_check(hy_conv_tails(f32_, at(proj_, w.off_a), ld_proj_, w.conv_ch, l.conv, tails_[run.state_idx], r, stream), "conv tails");
+            const int off_g = up8(l.heads * l.dim);
+            gemm(HY_STORE, at(proj_, w.off_c), ld_proj_, w.a2, p2_, ld_p2_, T, nullptr, 1.f);
+            gemm(HY_STORE, at(proj_, w.off_d), ld_proj_, w.g2, at(p2_, off_g), ld_p2_, T, nullptr, 1.f);
+            cuda_check(hy_delta_prep(f32_, d, conv_, ld_conv_, at(proj_, w.off_b), ld_proj_, p2_, ld_p2_, w.A_log, w.dt_bias, qq_, kk_, vv_, dec_, beta_, T, stream), "delta prep");
+            cuda_check(hy_recurrence(true, qq_, kk_, vv_, dec_, beta_, rec_, states_[run.state_idx], l.heads, l.kv_heads, l.dim, l.vdim, r, stream), "delta rule");
+            cuda_check(hy_gated_norm(f32_, rec_, l.heads * l.vdim, l.vdim, w.norm_w, l.vdim, at(p2_, off_g), ld_p2_, 0, 0, nullptr, 1, nullptr, 0, mix_, ld_mix_, hc_.eps, T, stream), "gated norm");
+        } else {
+            const HyMamba m{l.heads, l.vdim, l.state, l.groups};
+            const int inner = l.heads * l.vdim;
+            cuda_check(hy_conv_silu(f32_, at(proj_, w.off_b), ld_proj_, w.conv_ch, w.conv_w, w.conv_b, l.conv, conv_, ld_conv_, tails_[run.state_idx], r, stream), "conv");
+            cuda_check(hy_conv_tails(f32_, at(proj_, w.off_b), ld_proj_, w.conv_ch, l.conv, tails_[run.state_idx], r, stream), "conv tails");
+            cuda_check(hy_mamba_prep(f32_, m, conv_, ld_conv_, at(proj_, w.off_c), ld_proj_, w.A_log, w.dt_bias, qq_, kk_, vv_, dec_, T, stream), "mamba prep");
+            cuda_check(hy_recurrence(false, qq_, kk_, vv_, dec_, nullptr, rec_, states_[run.state_idx], l.heads, l.groups, l.state, l.vdim, r, stream), "state-space recurrence");
+            cuda_check(hy_gated_norm(f32_, rec_, inner, inner / l.norm_groups, w.norm_w, inner, at(proj_, w.off_a), ld_proj_, 1, 1, w.D, l.vdim, conv_, ld_conv_, mix_, ld_mix_,
+                                     hc_.eps, T, stream), "gated norm");
+        }
+        gemm(HY_ACC_F32, mix_, ld_mix_, w.o, x_, W, T, nullptr, 1.f);
+        if (l.moe.present) moe(w, l, r);
+        if (capture_layers) {
+            cuda_check(cudaStreamSynchronize(stream), "capture sync");
+            const size_t n0 = capture_layers->size(); capture_layers->resize(n0 + (size_t)T * W);
+            cuda_check(cudaMemcpy(capture_layers->data() + n0, x_, (size_t)T * W * 4, cudaMemcpyDeviceToHost), "capture D2H");
+        }
+    }
+    if (capture_layers == &dbg_buf) {
+        if (FILE* f = std::fopen(dbg_layers, "wb")) { std::fwrite(dbg_buf.data(), 4, dbg_buf.size(), f); std::fclose(f); }
+        capture_layers = nullptr;
+    }
+    if (NS > 0) {
+        cuda_check(hy_layernorm(f32_, x_, d_meta_ + o_samp, final_norm_, hs_, Wld_, NS, W, hc_.eps, stream), "final norm");
+        float* lg = logits_out ? logits_out : logits_;
+        gemm(HY_STORE_F32, hs_, Wld_, head_, lg, V, NS, nullptr, hc_.logit_scale);
+        cuda_check(hy_argmax_rows(lg, NS, V, d_out_ids_, stream), "argmax");
+        cuda_check(cudaMemcpyAsync(h_out_ids, d_out_ids_, (size_t)NS * 4, cudaMemcpyDeviceToHost, stream), "ids D2H");
+        d2h_bytes += (size_t)NS * 4;
+    }
+}
+
+std::unique_ptr<ModelBase> make_model(const ModelConfig& cfg, const EngineOptions& opt) {
+    if (cfg.arch == "ratasun") return std::unique_ptr<ModelBase>(new HybridModel(cfg, opt));
+    if (opt.f32) throw std::runtime_error("the Llama-family models run in bf16 only; float32 is available for the hybrid family");
+    return std::unique_ptr<ModelBase>(new DeviceModel(cfg, opt));
+}
+
+}  // namespace oa

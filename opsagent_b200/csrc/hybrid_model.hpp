@@ -1,0 +1,70 @@
+// hybrid_model.hpp — device-resident model of the hybrid decoder family (configuration: hybrid_config.hpp, kernels: hybrid_kernels.hpp).
+// It plugs into the same scheduler as the Llama-family DeviceModel: rows of a step arrive as a StepInput (prefill chunks and single decode
+// tokens alike), attention layers keep their compressed keys in the engine's 64-token pages, recurrent layers keep an fp32 state and their
+// convolution tails in the sequence's state slot.
+#pragma once
+#include <string>
+#include <vector>
+
+#include "hybrid_config.hpp"
+#include "hybrid_kernels.hpp"
+#include "model.hpp"
+
+namespace oa {
+
+class HybridModel : public ModelBase {
+public:
+    HybridModel(const ModelConfig& cfg, const EngineOptions& opt);
+    ~HybridModel() override;
+    void forward(const StepInput& in, float* logits_out) override;
+    // debug: copy of the residual stream after every layer execution of the NEXT forward ([runs, T, width] fp32, host); empty = off
+    std::vector<float>* capture_layers = nullptr;
+
+private:
+    struct Mat {                    // [N, ld] matrix in the activation type, ld = K rounded up to 8 (zero padded); B operand of C = A . B^T
+        void* p = nullptr; int N = 0, K = 0, ld = 0;
+        bool tc = false; CUtensorMap tm[4];           // tensor-core path (bf16): B-operand maps for BLOCK_N = 32, 64, 128, 256
+    };
+    struct HostMat { int N = 0, K = 0; std::vector<float> v; };
+    struct LayerW {
+        float* norm1 = nullptr;
+        Mat in, a2, g2, o, router;
+        int off_a = 0, off_b = 0, off_c = 0, off_d = 0;   // column offsets of the fused input projection's segments (see hybrid_model.cpp)
+        int a_rank = 0, g_rank = 0;
+        void *uk_t = nullptr, *uv = nullptr; float* dkv_norm = nullptr; int rope = -1;      // latent attention
+        float *A_log = nullptr, *dt_bias = nullptr, *norm_w = nullptr, *conv_w = nullptr, *conv_b = nullptr, *D = nullptr;
+        int conv_ch = 0;
+        float* correction = nullptr; void *gu = nullptr, *down = nullptr; int ffp = 0;       // experts: gu [E][2 ffp][ldw], down [E][W][ffp]
+        CUtensorMap tm_gu[2], tm_down[2]; bool moe_tc = false;                               // grouped tensor-core path: BLOCK_N = 128, 256
+    };
+    struct RopeTable { float base; int dims; float *cos = nullptr, *sin = nullptr; };
+
+    void* dmalloc(size_t bytes);
+    float* upload_f32(const std::vector<float>& v);
+    void* upload_act(const std::vector<float>& v);                        // in the activation type
+    Mat upload_mat(const HostMat& m);
+    HostMat tensor(const std::string& name, int N, int K);                // checkpoint tensor (or seeded values) as fp32 [N, K]; K == 0: any width
+    std::vector<float> vec(const std::string& name, int n, float init_mean, float init_spread);
+    void gemm(int mode, const void* A, int lda, const Mat& B, void* C, int ldc, int M, const float* bias, float alpha);
+    void moe(const LayerW& w, const HyLayer& l, const HyRows& r);
+
+    HybridConfig hc_; bool f32_ = false; size_t es_ = 2;
+    struct SafeTensorsHolder; SafeTensorsHolder* st_ = nullptr;
+    std::vector<void*> allocs_;
+    std::vector<LayerW> lw_; std::vector<RopeTable> ropes_;
+    void* embed_ = nullptr; Mat head_, loop_in_; float *loop_step_ = nullptr, *final_norm_ = nullptr;
+    std::vector<void*> caches_;                    // per attention execution: [num_pages * 64][kv_rank + rot_dim] in the activation type
+    std::vector<float*> states_; std::vector<void*> tails_;      // per recurrent execution: [slots][heads * dim * vdim] fp32, [slots][(taps - 1) * channels]
+    int MR_ = 0, MS_ = 0, Wld_ = 0;
+    // activations
+    float *x_ = nullptr, *x0_ = nullptr, *q_abs_ = nullptr, *qq_ = nullptr, *kk_ = nullptr, *vv_ = nullptr, *dec_ = nullptr, *beta_ = nullptr, *rec_ = nullptr, *wgt_ = nullptr,
+          *logits_ = nullptr, *moe_y_ = nullptr;
+    void *cat_ = nullptr, *h_ = nullptr, *proj_ = nullptr, *p2_ = nullptr, *conv_ = nullptr, *lat_ = nullptr, *mix_ = nullptr, *act_ = nullptr, *hs_ = nullptr, *moe_a_ = nullptr;
+    int ld_proj_ = 0, ld_p2_ = 0, ld_conv_ = 0, ld_mix_ = 0;
+    int32_t *idx_ = nullptr, *d_out_ids_ = nullptr, *tile_expert_ = nullptr, *row_src_ = nullptr, *n_tiles_ = nullptr, *dst_of_ = nullptr; int max_tiles_ = 0;
+    int32_t* h_meta_buf_[2] = {nullptr, nullptr}; cudaEvent_t meta_ev_[2] = {nullptr, nullptr}; int meta_idx_ = 0;
+    int32_t* d_meta_ = nullptr; size_t meta_cap_words_ = 0;
+    std::vector<int32_t> row_seq_, seq_pos0_;
+};
+
+}  // namespace oa

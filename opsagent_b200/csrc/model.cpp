@@ -69,7 +69,7 @@ struct DeviceGuard {
     ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
 };
 
-DeviceModel::DeviceModel(const ModelConfig& c, const EngineOptions& o) : cfg(c), opt(o) {
+DeviceModel::DeviceModel(const ModelConfig& c, const EngineOptions& o) : ModelBase(c, o) {
     DeviceGuard guard(opt.device);
     cuda_check(cudaSetDevice(opt.device), "cudaSetDevice");
     cudaDeviceProp prop;
@@ -308,12 +308,12 @@ DeviceModel::~DeviceModel() {
     if (stream) cudaStreamDestroy(stream);
 }
 
-const char* DeviceModel::kt_name(int id) {
+const char* ModelBase::kt_name(int id) {
     static const char* n[16] = {"h2d+embed", "rmsnorm", "qkv_gemm", "rope_kv", "attention", "attn_merge", "o_gemm", "resid_rmsnorm", "gate_up_gemm",
                                 "swiglu", "down_gemm", "gather+norm", "lm_head", "argmax+d2h", "", ""};
     return n[id & 15];
 }
-void DeviceModel::sync() { cuda_check(cudaStreamSynchronize(stream), "stream sync"); }
+void ModelBase::sync() { cuda_check(cudaStreamSynchronize(stream), "stream sync"); }
 
 // N-tile heuristic.  Decode (M <= 128) streams weights once: prefer the largest tile that still yields >= 1 CTA
 // per SM; prefill has M/128 row tiles as well, so the widest tile (least A re-reads) wins.

@@ -31,6 +31,9 @@ struct StepInput {
     // constrained row.  mask_updates = concatenated records {slot, words[mask_words]} to be written into the table before the LM head.
     std::vector<int32_t> mask_slots; std::vector<uint32_t> mask_updates;
     bool want_logits = false;                         // debug: fp32 logits of the sampled rows (tensor-parallel ranks stage their shard)
+    // models with per-sequence state: rows of sequence i are [seq_row0[i], seq_row0[i+1]) (always filled, rows of a sequence are contiguous)
+    // and state_slots[i] is its slot (-1 for models without state)
+    std::vector<int32_t> seq_row0, state_slots;
 };
 
 struct DecodePlan {
@@ -39,15 +42,16 @@ struct DecodePlan {
 // contiguous, balanced partition of all (sequence, kv head) page lists over n_ctas CTAs
 void build_decode_plan(const int32_t* ctx_lens, int n_seqs, int n_kv, int n_ctas_target, int force_splits, DecodePlan& out);
 
-class DeviceModel {
+// What the scheduler (engine.cpp) sees of a model: its step function, the geometry of its paged cache and of its per-sequence state slots,
+// the sampled ids of the last step, and counters.  make_model() picks the class from the configuration (the model registry).
+class ModelBase {
 public:
-    DeviceModel(const ModelConfig& cfg, const EngineOptions& opt);
-    ~DeviceModel();
-    DeviceModel(const DeviceModel&) = delete;
-
+    ModelBase(const ModelConfig& c, const EngineOptions& o) : cfg(c), opt(o) {}
+    virtual ~ModelBase() {}
+    ModelBase(const ModelBase&) = delete;
     // Runs one forward.  Greedy next-token ids of sample_rows land in h_out_ids (pinned) once the stream is
     // synchronised.  logits_out (device fp32 [n_sample, vocab]) is optional.
-    void forward(const StepInput& in, float* logits_out);
+    virtual void forward(const StepInput& in, float* logits_out) = 0;
     void sync();
     int32_t* h_out_ids = nullptr;        // pinned, [max_batch or max_step_tokens]
 
@@ -57,15 +61,24 @@ public:
     std::unique_ptr<TpComm> comm;
     cudaStream_t stream = nullptr;
     int num_pages = 0, max_pages_per_seq = 0, sm_count = 148;
+    int state_slots = 0;                 // > 0: sequences carry recurrent state in one of this many slots (no prefix reuse: a cached page cannot restore the state)
     int mask_words = 0, mask_slots = 0, max_mask_updates = 0;    // token-mask table geometry (words = ceil(vocab / 32))
     size_t weight_bytes = 0, kv_pool_bytes = 0;
-    KvLayout kv{}; CUtensorMap tm_kv;
     // instrumentation
     bool profile_attn = false; double attn_ms_accum = 0; std::vector<cudaEvent_t> ev;
     // in-situ per-kernel timing (events after every launch, warm caches, real launch gaps): OA_PROFILE_ALL=1
     bool profile_all = false; std::vector<cudaEvent_t> ev_all; std::vector<int> ev_ids; double kt_ms[16] = {0}; long kt_n[16] = {0};
     static const char* kt_name(int id);
     uint64_t h2d_bytes = 0, d2h_bytes = 0;
+};
+std::unique_ptr<ModelBase> make_model(const ModelConfig& cfg, const EngineOptions& opt);
+
+class DeviceModel : public ModelBase {
+public:
+    DeviceModel(const ModelConfig& cfg, const EngineOptions& opt);
+    ~DeviceModel() override;
+    void forward(const StepInput& in, float* logits_out) override;
+    KvLayout kv{}; CUtensorMap tm_kv;
 
     struct Layer { WeightMat qkv, o, gu, down; void *ln1 = nullptr, *ln2 = nullptr, *bqkv = nullptr; };
     std::vector<Layer> layers;

@@ -144,6 +144,21 @@ class Engine:
         _check(self._L.oa_debug_prefill_logits(self._h, toks.ctypes.data, len(toks), out.ctypes.data))
         return out
 
+    def trace_step(self, entries, end=()):
+        """One step of a token-level replay: entries = [(request id: int, next tokens, wanted places among them)], all run as one batch
+        from the cache and state earlier steps left; `end` lists request ids that are finished after it.  Returns fp32 logits [wanted, vocab]."""
+        import numpy as np
+        ids = np.array([e[0] for e in entries], dtype=np.int64)
+        ntok = np.array([len(e[1]) for e in entries], dtype=np.int32)
+        toks = np.array([t for e in entries for t in e[1]], dtype=np.int32)
+        nwant = np.array([len(e[2]) for e in entries], dtype=np.int32)
+        want = np.array([w for e in entries for w in e[2]], dtype=np.int32)
+        ends = np.array(list(end), dtype=np.int64)
+        out = np.empty((int(nwant.sum()), self.info["vocab"]), dtype=np.float32)
+        _check(self._L.oa_trace_step(self._h, len(entries), ids.ctypes.data, ntok.ctypes.data, toks.ctypes.data, nwant.ctypes.data, want.ctypes.data,
+                                     len(ends), ends.ctypes.data, out.ctypes.data, out.shape[0]))
+        return out
+
     def kernel_times(self, reset: bool = True) -> dict:
         buf = C.create_string_buffer(4096)
         _check(self._L.oa_debug_kernel_times(self._h, buf, 4096, int(reset)))
