@@ -1,0 +1,198 @@
+"""The Ratasun hybrid family on the GPU against the slow float64 oracle (tests/hybrid_oracle.py): every mixer alone, the router, looped blocks,
+and — through Engine.trace_step, the replay entry point that drives the scheduler's own batch builder, pages and state slots — prompts cut
+into portions, token-by-token decoding, mixed batches and reused pages / slots.  Small random checkpoints are written per test."""
+import numpy as np
+import pytest
+
+import hybrid_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 2e-4          # fp32 engine against the float64 oracle (relative to the logits' spread)
+BF16_TOL = 0.15         # bf16 matrices / activations; a row whose expert choice flips on a rounding may exceed it, so 90 % of rows must hold it
+SAME_TOL = 2e-3         # one engine, two schedules: a row's arithmetic does not depend on how its prompt was cut or on its batch
+
+
+def engine(folder, dtype="float32", pages=8, slots=4, **kw):
+    from opsagent_b200 import Engine
+    return Engine(dict({"model_dir": str(folder), "dtype": dtype, "num_pages": pages, "max_seq_len": 64 * pages, "max_step_tokens": 64 * pages,
+                        "max_batch": slots, "prefix_cache": 0}, **kw))
+
+
+def checkpoint(tmp_path, cfg, seed=0, **kw):
+    W = O.random_weights(cfg, seed, **kw)
+    O.write_checkpoint(str(tmp_path), cfg, W)
+    return W
+
+
+def tokens_of(cfg, n, seed):
+    return np.random.default_rng(seed).integers(0, cfg["vocab"], n).tolist()
+
+
+def replay(eng, rid, toks, cuts):
+    """feed toks to request rid in portions of the given sizes (the rest one by one), wanting every position; -> logits [len(toks), vocab]"""
+    out, at = [], 0
+    sizes = list(cuts)
+    while at < len(toks):
+        n = min(sizes.pop(0) if sizes else 1, len(toks) - at)
+        out.append(eng.trace_step([(rid, toks[at:at + n], list(range(n)))], [rid] if at + n == len(toks) else []))
+        at += n
+    return np.concatenate(out)
+
+
+def check(got, want, dtype):
+    e = O.rel_err(got.astype(np.float64), want)
+    if dtype == "float32":
+        assert e.max() < F32_TOL, f"worst row {e.argmax()} differs by {e.max():.3e}"
+    else:
+        assert np.quantile(e, 0.9) < BF16_TOL and np.median(e) < BF16_TOL / 4, f"bf16 rows differ: median {np.median(e):.3e}, 90% {np.quantile(e, 0.9):.3e}"
+
+
+MOE = O.moe()
+SINGLE = {
+    "attention": [O.attention_layer()],
+    "attention_partial_rotation_base": [O.attention_layer(heads=3, dim=12, rot_dim=4, vdim=10, kv_rank=20, base=50.0)],
+    "delta": [O.delta_layer()],
+    "delta_equal_heads": [O.delta_layer(heads=2, kv_heads=2, dim=8, vdim=8, conv=2)],
+    "mamba": [O.mamba_layer()],
+    "mamba_one_group_three_norm_groups": [O.mamba_layer(heads=3, vdim=8, state=12, groups=1, norm_groups=3, conv=5)],
+    "attention_moe": [O.attention_layer(mlp=MOE)],
+    "moe_top1_all_groups": [O.mamba_layer(mlp=O.moe(experts=4, top=1, groups=2, keep=2, ff=16, scale=1.0))],
+    "moe_single_member_groups": [O.delta_layer(mlp=O.moe(experts=5, top=2, groups=5, keep=3, ff=20, scale=2.5))],
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(SINGLE))
+def test_each_mechanism_alone(tmp_path, name, dtype):
+    cfg = O.make_config(SINGLE[name], width=40, vocab=77, logit_scale=1.5)
+    W = checkpoint(tmp_path, cfg, seed=len(name))
+    toks = tokens_of(cfg, 70, 1)                       # crosses a page border
+    want = O.forward(cfg, W, toks)
+    with engine(tmp_path, dtype) as eng:
+        check(replay(eng, 1, toks, [70]), want, dtype)           # whole prompt
+        check(replay(eng, 2, toks, [1, 1, 2, 3, 57, 2]), want, dtype)   # the first tokens alone, short portions, then token by token
+
+
+def hybrid_cfg(loop=True):
+    layers = [O.attention_layer(mlp=MOE), O.delta_layer(mlp=MOE), O.mamba_layer(mlp=None), O.attention_layer(heads=1, dim=8, rot_dim=8, vdim=32, kv_rank=16, mlp=MOE)]
+    return O.make_config(layers, loop={"start": 1, "stop": 3, "times": 2} if loop else None, logit_scale=2.0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_portions_and_decoding_match_the_whole_prompt(tmp_path, dtype):
+    cfg = hybrid_cfg()
+    W = checkpoint(tmp_path, cfg, seed=3)
+    toks = tokens_of(cfg, 140, 2)
+    want = O.forward(cfg, W, toks)
+    with engine(tmp_path, dtype) as eng:
+        for cuts in ([140], [2, 62, 1, 2, 61, 12], [63, 2, 64], [5], [127, 1, 1, 11], [64, 64, 2, 2, 2, 2, 2, 2]):
+            check(replay(eng, 7, toks, cuts), want, dtype)
+
+
+def test_looped_attention_has_a_cache_per_pass_and_no_loop_runs(tmp_path):
+    layers = [O.delta_layer(mlp=MOE), O.attention_layer(mlp=None), O.mamba_layer(mlp=MOE)]
+    for k, loop in enumerate([{"start": 0, "stop": 3, "times": 3}, {"start": 1, "stop": 2, "times": 1}, None]):
+        cfg = O.make_config(layers, width=56, vocab=90, loop=loop)
+        folder = tmp_path / str(k)
+        W = checkpoint(folder, cfg, seed=10 + k)
+        toks = tokens_of(cfg, 75, 4)
+        with engine(folder) as eng:
+            check(replay(eng, 1, toks, [3, 61, 2]), O.forward(cfg, W, toks), "float32")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_unequal_requests_in_one_batch_and_reused_pages_and_slots(tmp_path, dtype):
+    """Three requests at different stages share every step (a prompt portion beside single tokens); then later requests take over the pages
+    and the two state slots of finished ones: a stale state or cache row would show."""
+    cfg = hybrid_cfg()
+    W = checkpoint(tmp_path, cfg, seed=5)
+    lens = {1: 100, 2: 37, 3: 66, 4: 90, 5: 20}
+    toks = {r: tokens_of(cfg, n, 20 + r) for r, n in lens.items()}
+    want = {r: O.forward(cfg, W, toks[r]) for r in lens}
+    got = {r: [] for r in lens}
+    at = {r: 0 for r in lens}
+    with engine(tmp_path, dtype, pages=4, slots=2) as eng:
+        def step(parts):
+            entries, end = [], []
+            for r, n in parts:
+                n = min(n, lens[r] - at[r])
+                entries.append((r, toks[r][at[r]:at[r] + n], list(range(n))))
+                at[r] += n
+                if at[r] == lens[r]:
+                    end.append(r)
+            out = eng.trace_step(entries, end)
+            k = 0
+            for r, t, w in entries:
+                got[r].append(out[k:k + len(w)])
+                k += len(w)
+        step([(1, 60)])
+        step([(1, 1), (2, 30)])                       # 1 decodes beside a portion of 2
+        step([(1, 3), (2, 7)])                        # 2 ends: its page and slot are free
+        step([(1, 36), (5, 2)])                       # 1 ends, 5 starts in 2's slot
+        step([(5, 18), (3, 64)])                      # 5 ends; 3 takes 1's slot, filling exactly one page
+        step([(3, 2), (4, 2)])                        # 3 ends on a page's second token; 4 starts
+        while at[4] < lens[4]:
+            step([(4, 29)])
+        assert eng.stats()["pages_free"] == 4
+        for r in lens:                                # each alone, whole, in the same engine: the same rows up to rounding
+            alone = replay(eng, 10 + r, toks[r], [lens[r]])
+            assert O.rel_err(np.concatenate(got[r]).astype(np.float64), alone.astype(np.float64)).max() < SAME_TOL
+    for r in lens:
+        check(np.concatenate(got[r]), want[r], dtype)
+
+
+def test_a_far_key_decides_and_is_found_through_pages_and_decoding(tmp_path):
+    """Sharp attention: single keys dominate, also hundreds of tokens back.  The oracle itself shows the sensitivity (without the first page
+    the answer changes by far more than the tolerance), and the engine must agree with it in prompts and in decoding."""
+    cfg = O.make_config([O.attention_layer(heads=2, dim=16, rot_dim=8, vdim=16, kv_rank=24, base=500000.0), O.attention_layer(mlp=MOE)], width=48, vocab=64)
+    W = checkpoint(tmp_path, cfg, seed=8, sharp=7.0)
+    toks = tokens_of(cfg, 330, 6)
+    want = O.forward(cfg, W, toks)
+    without_first_page = O.forward(cfg, W, toks[64:])
+    assert O.rel_err(without_first_page[-40:], want[-40:]).max() > 50 * F32_TOL
+    with engine(tmp_path, pages=6) as eng:
+        check(replay(eng, 1, toks, [330]), want, "float32")
+        check(replay(eng, 2, toks, [255, 2, 63]), want, "float32")      # decodes across the borders at 256 and 320
+
+
+def test_long_decoding(tmp_path):
+    cfg = hybrid_cfg()
+    W = checkpoint(tmp_path, cfg, seed=9)
+    toks = tokens_of(cfg, 200, 7)
+    with engine(tmp_path) as eng:
+        check(replay(eng, 1, toks, [3]), O.forward(cfg, W, toks), "float32")     # 197 single-token steps over three page borders
+
+
+def test_bf16_tensor_core_path_and_plain_path_agree_with_the_oracle(tmp_path):
+    cfg = hybrid_cfg()
+    W = checkpoint(tmp_path, cfg, seed=11)
+    toks = tokens_of(cfg, 150, 8)
+    want = O.forward(cfg, W, toks)
+    for tc in (0, 1):
+        with engine(tmp_path, "bfloat16", hy_tensor_core=tc) as eng:
+            check(replay(eng, 1, toks, [150]), want, "bfloat16")
+            check(replay(eng, 2, toks, [130]), want, "bfloat16")
+
+
+def test_greedy_generation_through_the_scheduler(tmp_path):
+    """oa_tokens_submit -> continuous batching -> greedy sampling: three requests on two state slots (one waits for a slot), each compared
+    with the oracle's greedy continuation wherever the oracle's top-1 margin is not a near tie."""
+    cfg = hybrid_cfg()
+    W = checkpoint(tmp_path, cfg, seed=12)
+    prompts = [tokens_of(cfg, n, 30 + n) for n in (9, 70, 33)]
+    n_new = 12
+    with engine(tmp_path, pages=6, slots=2) as eng:
+        tickets = [eng.tokens_submit(p, n_new, flags=1) for p in prompts]
+        outs = [eng.wait(t).token_ids for t in tickets]
+        assert eng.stats()["pages_free"] == 6
+    for p, out in zip(prompts, outs):
+        seq = list(p)
+        assert len(out) == n_new
+        for tok in out:
+            lg = O.forward(cfg, W, seq)[-1]
+            top2 = np.sort(lg)[-2:]
+            if int(np.argmax(lg)) != tok:
+                assert top2[1] - top2[0] < 1e-3, "greedy token differs from the oracle's outside a near tie"
+                break
+            seq.append(tok)
