@@ -66,6 +66,12 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tcgen05_kernel(const __grid
         m_blk = m0 + within % rows; n_blk = within / rows;
     }
     const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
+    int b_row0 = n_blk * BN;
+    if (p.m_tile_group) {                 // grouped product: the tile table may come from the preceding kernel, so nothing is prefetched ahead of it
+        griddep_wait();
+        if (m_blk >= *p.n_m_tiles) return;
+        b_row0 += p.m_tile_group[m_blk] * p.group_rows;
+    }
 
     if (warp == 0 && lane == 0) {
         tma_prefetch_desc(&tmA);
@@ -87,7 +93,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tcgen05_kernel(const __grid
             const int pre = num_kb < STAGES ? num_kb : STAGES;
             for (int kb = 0; kb < pre; ++kb) {
                 mbar_expect_tx(&full_bar[kb], Cfg::STAGE_BYTES);
-                tma_load_2d(smem + kb * Cfg::STAGE_BYTES + Cfg::A_BYTES, &tmB, &full_bar[kb], kb * BLOCK_K, n_blk * BN, kEvictFirst);
+                tma_load_2d(smem + kb * Cfg::STAGE_BYTES + Cfg::A_BYTES, &tmB, &full_bar[kb], kb * BLOCK_K, b_row0, kEvictFirst);
             }
             griddep_wait();
             for (int kb = 0; kb < pre; ++kb)
@@ -99,7 +105,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tcgen05_kernel(const __grid
                 uint8_t* b_dst = a_dst + Cfg::A_BYTES;
                 mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
                 tma_load_2d(a_dst, &tmA, &full_bar[s], kb * BLOCK_K, m_blk * BLOCK_M, kEvictLast);
-                tma_load_2d(b_dst, &tmB, &full_bar[s], kb * BLOCK_K, n_blk * BN, kEvictFirst);
+                tma_load_2d(b_dst, &tmB, &full_bar[s], kb * BLOCK_K, b_row0, kEvictFirst);
                 if (++s == STAGES) { s = 0; ph ^= 1; }
             }
         }
@@ -195,6 +201,20 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tcgen05_kernel(const __grid
                     *reinterpret_cast<uint4*>(orow) = o0;
                     *reinterpret_cast<uint4*>(orow + 8) = o1;
                 }
+            } else if (EPI == EPI_F32) {
+                if (row_ok) {
+                    float* orow = p.f32_out + (size_t)row * p.ldf;
+                    const float al = p.alpha == 0.f ? 1.f : p.alpha;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        if (col0 + j < p.N) {
+                            float4 o = make_float4(__uint_as_float(v[j]) * al, __uint_as_float(v[j + 1]) * al, __uint_as_float(v[j + 2]) * al, __uint_as_float(v[j + 3]) * al);
+                            if (p.bias_f32) { const float4 b = *reinterpret_cast<const float4*>(p.bias_f32 + col0 + j); o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w; }
+                            if (p.f32_accumulate) { const float4 r = *reinterpret_cast<const float4*>(orow + col0 + j); o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w; }
+                            *reinterpret_cast<float4*>(orow + col0 + j) = o;
+                        }
+                    }
+                }
             } else {  // EPI_LOGITS
                 if (row_ok) {
                     if (mask_row) {
@@ -261,6 +281,7 @@ static cudaError_t launch_bn(const CUtensorMap* tmA, const CUtensorMap* tmB, con
         case EPI_RESID: return launch_one<BN, EPI_RESID>(tmA, tmB, p, s);
         case EPI_SWIGLU: return launch_one<BN, EPI_SWIGLU>(tmA, tmB, p, s);
         case EPI_LOGITS: return launch_one<BN, EPI_LOGITS>(tmA, tmB, p, s);
+        case EPI_F32: return launch_one<BN, EPI_F32>(tmA, tmB, p, s);
     }
     return cudaErrorInvalidValue;
 }
@@ -276,7 +297,8 @@ cudaError_t launch_gemm(const CUtensorMap* tmA, const CUtensorMap* tmB, const Ge
     if (p.M <= 0 || p.N <= 0 || p.K <= 0 || (p.N % 8) != 0 || (p.K % 8) != 0) return cudaErrorInvalidValue;
     if (epilogue == EPI_SWIGLU && (p.N % 32) != 0) return cudaErrorInvalidValue;
     // large-M (prefill) shapes with the widest tile go to the persistent kernel (epilogue overlapped with the next tile)
-    if (block_n == 256 && epilogue != EPI_LOGITS && !persistent_disabled() &&
+    if (epilogue == EPI_F32 && ((p.ldf % 4) != 0 || !p.f32_out)) return cudaErrorInvalidValue;
+    if (block_n == 256 && epilogue != EPI_LOGITS && epilogue != EPI_F32 && !p.m_tile_group && !persistent_disabled() &&
         (long long)((p.N + 255) / 256) * ((p.M + BLOCK_M - 1) / BLOCK_M) >= persistent_min_tiles()) {
         switch (epilogue) {
             case EPI_STORE: return launch_persistent<EPI_STORE>(tmA, tmB, p, stream);

@@ -135,7 +135,7 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
     final_norm_ = upload_f32(vec("final.norm", W, 1.f, 0.1f));
     if (hc_.loop_times > 0) { loop_in_ = upload_mat(tensor("loop.in", W, 2 * W)); loop_step_ = upload_f32(vec("loop.step", hc_.loop_times * W, 0.f, 0.1f)); }
     lw_.resize(hc_.layers.size());
-    int max_in = 8, max_p2 = 8, max_conv = 8, max_mix = 8, max_qabs = 8, max_lat = 8, max_qk = 8, max_v = 8, max_dec = 8, max_h = 8, max_act = 8, max_top = 1, max_E = 1;
+    int max_in = 8, max_p2 = 8, max_conv = 8, max_mix = 8, max_qabs = 8, max_lat = 8, max_qk = 8, max_v = 8, max_dec = 8, max_h = 8, max_act = 8, max_top = 1, max_E = 1, max_ffp = 16;
     for (size_t li = 0; li < hc_.layers.size(); ++li) {
         const HyLayer& l = hc_.layers[li]; LayerW& w = lw_[li];
         const std::string p = "l" + std::to_string(li) + ".", mx = p + "mix.";
@@ -217,6 +217,15 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
                 for (int n = 0; n < W; ++n) std::memcpy(&dn[((size_t)e * W + n) * w.ffp], &d.v[(size_t)n * m.ff], (size_t)m.ff * 4);
             }
             w.gu = upload_act(gu); w.down = upload_act(dn);
+            if (!f32_ && opt.hy_tensor_core && W % 8 == 0) {
+                w.moe_tc = true;
+                for (int i = 0; i < 2; ++i) {
+                    const uint32_t bn = i ? 256 : 128;
+                    if (make_tmap_bf16_2d(&w.tm_gu[i], w.gu, (uint64_t)m.experts * 2 * w.ffp, (uint64_t)Wld_, (uint64_t)Wld_, bn, 64) != 0 ||
+                        make_tmap_bf16_2d(&w.tm_down[i], w.down, (uint64_t)m.experts * W, (uint64_t)w.ffp, (uint64_t)w.ffp, bn, 64) != 0) w.moe_tc = false;
+                }
+            }
+            max_ffp = std::max(max_ffp, w.ffp);
             max_act = std::max(max_act, m.top * w.ffp); max_top = std::max(max_top, m.top); max_E = std::max(max_E, m.experts);
         }
     }
@@ -232,7 +241,15 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
     q_abs_ = (float*)dmalloc(MR * max_qabs * 4); lat_ = dmalloc(MR * up8(max_lat) * es_);
     qq_ = (float*)dmalloc(MR * max_qk * 4); kk_ = (float*)dmalloc(MR * max_qk * 4); vv_ = (float*)dmalloc(MR * max_v * 4); rec_ = (float*)dmalloc(MR * max_v * 4);
     dec_ = (float*)dmalloc(MR * max_dec * 4); beta_ = (float*)dmalloc(MR * max_h * 4);
-    idx_ = (int32_t*)dmalloc(MR * max_top * 4); wgt_ = (float*)dmalloc(MR * max_top * 4); act_ = dmalloc(MR * max_act * es_);
+    idx_ = (int32_t*)dmalloc(MR * max_top * 4); wgt_ = (float*)dmalloc(MR * max_top * 4);
+    max_tiles_ = (int)((MR * max_top + 127) / 128) + max_E;
+    bool any_moe_tc = false; for (const LayerW& w : lw_) any_moe_tc |= w.moe_tc;
+    act_ = dmalloc(std::max(MR * max_act, any_moe_tc ? (size_t)max_tiles_ * 128 * max_ffp : 0) * es_);
+    if (any_moe_tc) {
+        moe_a_ = dmalloc((size_t)max_tiles_ * 128 * Wld_ * 2); moe_y_ = (float*)dmalloc((size_t)max_tiles_ * 128 * W * 4);
+        tile_expert_ = (int32_t*)dmalloc((size_t)max_tiles_ * 4); row_src_ = (int32_t*)dmalloc((size_t)max_tiles_ * 128 * 4);
+        n_tiles_ = (int32_t*)dmalloc(16); dst_of_ = (int32_t*)dmalloc(MR * max_top * 4);
+    }
     hs_ = dmalloc((size_t)MS_ * Wld_ * es_); logits_ = (float*)dmalloc((size_t)MS_ * V * 4); d_out_ids_ = (int32_t*)dmalloc((size_t)MS_ * 4);
     cuda_check(cudaMallocHost(&h_out_ids, (size_t)MS_ * 4), "cudaMallocHost");
     mask_words = (V + 31) / 32; mask_slots = 0; max_mask_updates = 0;       // grammar-constrained sampling is not wired to this family's head
@@ -267,7 +284,6 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
         cuda_check(cudaEventCreateWithFlags(&meta_ev_[i], cudaEventDisableTiming), "cudaEventCreate meta");
     }
     d_meta_ = (int32_t*)dmalloc(meta_cap_words_ * 4);
-    (void)max_E;
     cuda_check(cudaStreamSynchronize(stream), "init sync");
 }
 
@@ -281,14 +297,55 @@ HybridModel::~HybridModel() {
     delete st_;
 }
 
+// N-tile of the tensor-core GEMM: the widest tile that still gives about one CTA per SM (half of them for one or two row tiles)
+static int pick_tile_n(int M, int N, int sms) {
+    const int m_tiles = (M + 127) / 128;
+    const long long want = m_tiles <= 2 ? sms / 2 : sms;
+    for (int bn : {256, 128, 64, 32}) if ((long long)((N + bn - 1) / bn) * m_tiles >= want) return bn;
+    return 32;
+}
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 void HybridModel::gemm(int mode, const void* A, int lda, const Mat& B, void* C, int ldc, int M, const float* bias, float alpha) {
-    cuda_check(hy_gemm(f32_, mode, A, lda, B.p, B.ld, C, ldc, M, B.N, B.K, bias, alpha, 1, 0, 0, 0, stream), "gemm");
+    // bf16: the framework's tcgen05 tile GEMM (TMA operands, fp32 accumulator in TMEM) wherever pitches and pointers fit its 16-byte rules;
+    // a bf16 store may write the columns up to N rounded up to 8 (every such output has that room), an fp32 output needs N itself to fit
+    bool tc = B.tc && !f32_ && lda % 8 == 0 && aligned16(A) && lda >= B.ld;
+    if (mode == HY_STORE) tc = tc && ldc % 8 == 0 && aligned16(C) && !bias && alpha == 1.f;
+    else tc = tc && B.N % 8 == 0 && ldc % 4 == 0 && aligned16(C) && (!bias || aligned16(bias));
+    CUtensorMap tmA;
+    if (tc && make_tmap_bf16_2d(&tmA, A, (uint64_t)M, (uint64_t)B.ld, (uint64_t)lda, 128, 64) != 0) tc = false;
+    if (!tc) { cuda_check(hy_gemm(f32_, mode, A, lda, B.p, B.ld, C, ldc, M, B.N, B.K, bias, alpha, 1, 0, 0, 0, stream), "gemm"); return; }
+    GemmParams g{}; g.M = M; g.N = up8(B.N); g.K = B.ld;
+    const int bn = pick_tile_n(M, g.N, sm_count);
+    if (mode == HY_STORE) { g.out = C; g.ldo = ldc; cuda_check(launch_gemm(&tmA, &B.tm[bn == 32 ? 0 : bn == 64 ? 1 : bn == 128 ? 2 : 3], g, EPI_STORE, bn, stream), "gemm (tcgen05)"); return; }
+    g.f32_out = reinterpret_cast<float*>(C); g.ldf = ldc; g.f32_accumulate = mode == HY_ACC_F32; g.alpha = alpha; g.bias_f32 = bias;
+    cuda_check(launch_gemm(&tmA, &B.tm[bn == 32 ? 0 : bn == 64 ? 1 : bn == 128 ? 2 : 3], g, EPI_F32, bn, stream), "gemm (tcgen05, fp32 out)");
 }
 
 void HybridModel::moe(const LayerW& w, const HyLayer& l, const HyRows& r) {
     const HyMoe& m = l.moe; const int W = hc_.width, T = r.T;
     HyRouter hr{m.experts, m.top, m.groups, m.keep, m.scale};
     cuda_check(hy_moe_router(f32_, hr, h_, Wld_, w.router.p, w.router.ld, w.correction, W, idx_, wgt_, T, stream), "router");
+    if (w.moe_tc && T >= opt.hy_moe_grouped_rows) {
+        // prefill-sized batches: rows sorted by expert into 128-row tiles, two grouped tcgen05 GEMMs (SwiGLU in the first one's epilogue),
+        // then each token adds its choices' rows in choice order
+        const int bound = std::min(max_tiles_, (T * m.top + 127) / 128 + std::min(m.experts, T * m.top));
+        cuda_check(hy_moe_plan(idx_, T, m.top, m.experts, tile_expert_, row_src_, n_tiles_, dst_of_, bound, stream), "expert plan");
+        cuda_check(hy_moe_gather(h_, Wld_, Wld_, row_src_, n_tiles_, m.top, moe_a_, bound, stream), "expert gather");
+        CUtensorMap tmA, tmB;
+        if (make_tmap_bf16_2d(&tmA, moe_a_, (uint64_t)bound * 128, (uint64_t)Wld_, (uint64_t)Wld_, 128, 64) != 0 ||
+            make_tmap_bf16_2d(&tmB, act_, (uint64_t)bound * 128, (uint64_t)w.ffp, (uint64_t)w.ffp, 128, 64) != 0) throw std::runtime_error("tensor map for the expert activations failed");
+        GemmParams g{}; g.M = bound * 128; g.N = 2 * w.ffp; g.K = Wld_; g.out = act_; g.ldo = w.ffp;
+        g.m_tile_group = tile_expert_; g.n_m_tiles = n_tiles_; g.group_rows = 2 * w.ffp;
+        const int bn1 = 2 * w.ffp >= 256 ? 256 : 128;
+        cuda_check(launch_gemm(&tmA, &w.tm_gu[bn1 == 256], g, EPI_SWIGLU, bn1, stream), "experts gate/up (grouped tcgen05)");
+        GemmParams d{}; d.M = bound * 128; d.N = W; d.K = w.ffp; d.f32_out = moe_y_; d.ldf = W; d.alpha = 1.f;
+        d.m_tile_group = tile_expert_; d.n_m_tiles = n_tiles_; d.group_rows = W;
+        const int bn2 = W >= 256 ? 256 : 128;
+        cuda_check(launch_gemm(&tmB, &w.tm_down[bn2 == 256], d, EPI_F32, bn2, stream), "experts down (grouped tcgen05)");
+        cuda_check(hy_moe_combine(moe_y_, W, dst_of_, wgt_, m.top, x_, W, T, stream), "expert combine");
+        return;
+    }
     cuda_check(hy_moe_gate_up(f32_, h_, Wld_, w.gu, Wld_, W, m.ff, w.ffp, idx_, m.top, act_, T, stream), "experts gate/up");
     cuda_check(hy_moe_down(f32_, act_, w.down, W, w.ffp, idx_, wgt_, m.top, x_, T, stream), "experts down");
 }

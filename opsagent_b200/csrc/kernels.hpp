@@ -20,6 +20,7 @@ enum GemmEpilogue : int {
     EPI_RESID = 1,    // out[M,N] bf16 = acc + resid[M,N]      (out may alias resid)
     EPI_SWIGLU = 2,   // out[M,N/2] bf16 = silu(gate)*up, B rows interleaved 16 gate / 16 up
     EPI_LOGITS = 3,   // per-row (max, argmax) partial per N-tile -> argmax_ws; optional fp32 logits store
+    EPI_F32 = 4,      // f32_out[M,N] fp32 = alpha * acc (+ bias_f32[N]) (+ f32_out when f32_accumulate): fp32 residual streams and logits
 };
 struct GemmParams {
     int M, N, K;
@@ -31,6 +32,10 @@ struct GemmParams {
     // grammar-constrained rows (EPI_LOGITS): row r with mask_slot[r] >= 0 takes its arg-max only over the token ids whose bit is set in
     // mask_table[mask_slot[r] * mask_words ...]; bit index = col_offset + column (col_offset: first global id of a vocab-parallel shard)
     const uint32_t* mask_table; const int32_t* mask_slot; int mask_words, col_offset;
+    float* f32_out; int ldf; int f32_accumulate; float alpha; const float* bias_f32;     // EPI_F32 (alpha == 0 is read as 1)
+    // grouped product (routed experts): row tile m uses the B rows of group m_tile_group[m] (B = the groups' [group_rows, K] matrices stacked);
+    // row tiles >= *n_m_tiles do nothing.  Both live on the device and may come from the preceding kernel.
+    const int32_t* m_tile_group; const int32_t* n_m_tiles; int group_rows;
 };
 // tmA: box {64, 128} over A[M,K]; tmB: box {64, block_n} over B[N,K].  block_n in {32,64,128,256}.
 cudaError_t launch_gemm(const CUtensorMap* tmA, const CUtensorMap* tmB, const GemmParams& p, int epilogue, int block_n,
