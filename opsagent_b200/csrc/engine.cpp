@@ -284,7 +284,8 @@ public:
                 }
             }
             cudaEvent_t e0, e1; cudaEventCreate(&e0); cudaEventCreate(&e1);
-            const bool prof_all = model_.profile_all; model_.profile_all = false;      // in-situ kernel timing covers the decode steps only
+            const bool prof_prefill_all = std::getenv("OA_PROFILE_PREFILL") != nullptr;      // in-situ kernel timing of the prefill chunks instead of the decode steps
+            const bool prof_all = model_.profile_all && !prof_prefill_all; model_.profile_all = model_.profile_all && prof_prefill_all;
             // ---- prefill: ctx_len-1 tokens per sequence, chunked by the step token budget ----
             const int P = ctx_len - 1;
             cudaEventRecord(e0, model_.stream);
@@ -875,8 +876,9 @@ int oa_debug_kernel_times(oa_engine* h, char* buf, size_t n, int32_t reset) {
     if (!h || !buf) return fail(OA_ERR_BAD_REQUEST, "null argument");
     ModelBase& m = h->e->model();
     std::string s = "{";
-    for (int i = 0; i < 14; ++i) {
-        char t[128]; std::snprintf(t, sizeof t, "%s\"%s\": [%.4f, %ld]", i ? ", " : "", ModelBase::kt_name(i), m.kt_ms[i], m.kt_n[i]); s += t;
+    for (int i = 0; i < 16; ++i) {
+        if (!m.kt_name(i)[0]) continue;
+        char t[128]; std::snprintf(t, sizeof t, "%s\"%s\": [%.4f, %ld]", s.size() > 1 ? ", " : "", m.kt_name(i), m.kt_ms[i], m.kt_n[i]); s += t;
         if (reset) { m.kt_ms[i] = 0; m.kt_n[i] = 0; }
     }
     s += "}";

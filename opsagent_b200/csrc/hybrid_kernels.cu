@@ -5,6 +5,7 @@
 
 #include "hybrid_kernels.hpp"
 #include "kernels.hpp"
+#include "common.cuh"
 
 namespace oa {
 
@@ -183,6 +184,130 @@ __global__ void __launch_bounds__(128) hy_mla_attention_kernel(HyLatentAttn a, c
 #pragma unroll
         for (int w = 0; w < 4; ++w) v += f[w] * macc[w * R + c];
         stf(lat_out + ((long long)t * a.heads + h) * R + c, v * inv);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// latent attention on the tensor cores (bf16): one CTA owns 64 queries — consecutive (row, head) pairs of ONE sequence, so all of them read
+// the same cached rows — and streams that sequence's cache in 32-row tiles through a double-buffered cp.async ring.  S = Q K^T and
+// O += P V are mma.sync m16n8k16 products on the same shared-memory tile (the cached row is key AND value); softmax is online, in fp32
+// registers, with the mask applied per query position.  A CTA accumulates NVB * 8 of the latent's channels (blockIdx.y picks which).
+// ---------------------------------------------------------------------------------------------------------------------------------
+constexpr int MLA_MQ = 64, MLA_KT = 32;
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
+}
+template <int NVB>
+__global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn a, const float* __restrict__ q_abs, const __nv_bfloat16* __restrict__ cache,
+                                                                   __nv_bfloat16* __restrict__ lat_out, HyRows r, const int32_t* __restrict__ tile_seq,
+                                                                   const int32_t* __restrict__ tile_q0) {
+    extern __shared__ __align__(16) uint8_t mla_smem[];
+    const int R = a.kv_rank, E = R + a.rot_dim, EP = E + 8, H = a.heads;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(mla_smem);      // [MLA_MQ][EP]
+    __nv_bfloat16* Ks = Qs + MLA_MQ * EP;                                // [2][MLA_KT][EP]
+    int* qpos = reinterpret_cast<int*>(Ks + 2 * MLA_KT * EP);            // [MLA_MQ]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int seq = tile_seq[blockIdx.x], q0 = tile_q0[blockIdx.x], vbase = blockIdx.y * NVB * 8;
+    const int row0 = r.seq_row0[seq], len = r.seq_row0[seq + 1] - row0;
+    const int nq = min(MLA_MQ, len * H - q0);
+    const float qscale = a.scale * 1.4426950408889634f;
+    for (int idx = tid; idx < MLA_MQ * (E / 2); idx += 128) {
+        const int qi = idx / (E / 2), e = (idx - qi * (E / 2)) * 2;
+        float2 v = make_float2(0.f, 0.f);
+        if (qi < nq) { const int row = row0 + (q0 + qi) / H, h = (q0 + qi) % H; v = *reinterpret_cast<const float2*>(q_abs + ((long long)row * H + h) * E + e); }
+        *reinterpret_cast<uint32_t*>(Qs + qi * EP + e) = pack_bf16x2(v.x * qscale, v.y * qscale);
+    }
+    for (int qi = tid; qi < MLA_MQ; qi += 128) qpos[qi] = qi < nq ? r.positions[row0 + (q0 + qi) / H] : 0;
+    const int max_pos = r.positions[row0 + (q0 + nq - 1) / H];
+    const int n_kt = max_pos / MLA_KT + 1;
+    const int32_t* bt = r.block_tables + (long long)seq * r.max_pages_per_seq;
+    auto load_tile = [&](int kt, int buf) {
+        const int chunks = E / 8;
+        for (int idx = tid; idx < MLA_KT * chunks; idx += 128) {
+            const int j = idx / chunks, c = idx - j * chunks, key = kt * MLA_KT + j;
+            __nv_bfloat16* dst = Ks + (buf * MLA_KT + j) * EP + c * 8;
+            if (key <= max_pos) cp_async16(dst, cache + ((long long)bt[key >> 6] * 64 + (key & 63)) * E + c * 8);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float o[NVB][4];
+#pragma unroll
+    for (int i = 0; i < NVB; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    const bool active = 16 * warp < nq;
+    load_tile(0, 0);
+    for (int kt = 0; kt < n_kt; ++kt) {
+        if (kt + 1 < n_kt) { load_tile(kt + 1, (kt + 1) & 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        if (active) {
+            const __nv_bfloat16* Kb = Ks + (kt & 1) * MLA_KT * EP;
+            float s[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+            const uint32_t qa = smem_u32(Qs + (16 * warp + (lane & 15)) * EP + (lane >> 4) * 8);
+            const uint32_t ka = smem_u32(Kb + ((lane >> 4) * 8 + (lane & 7)) * EP + ((lane >> 3) & 1) * 8);
+            for (int ks = 0; ks < E / 16; ++ks) {
+                uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                ldmatrix_x4(qa + ks * 32, a0, a1, a2, a3);
+                ldmatrix_x4(ka + ks * 32, b0, b1, b2, b3);
+                mma_bf16_16816(s[0], a0, a1, a2, a3, b0, b1); mma_bf16_16816(s[1], a0, a1, a2, a3, b2, b3);
+                ldmatrix_x4(ka + 16 * EP * 2 + ks * 32, b0, b1, b2, b3);
+                mma_bf16_16816(s[2], a0, a1, a2, a3, b0, b1); mma_bf16_16816(s[3], a0, a1, a2, a3, b2, b3);
+            }
+            const int p_lo = qpos[16 * warp + (lane >> 2)], p_hi = qpos[16 * warp + (lane >> 2) + 8];
+            float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+            for (int nb = 0; nb < 4; ++nb)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int key = kt * MLA_KT + nb * 8 + (lane & 3) * 2 + (c & 1);
+                    if (key > (c < 2 ? p_lo : p_hi)) s[nb][c] = -INFINITY;
+                    if (c < 2) mx_lo = fmaxf(mx_lo, s[nb][c]); else mx_hi = fmaxf(mx_hi, s[nb][c]);
+                }
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1)); mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)); mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+            const float n_lo = fmaxf(m_lo, mx_lo), n_hi = fmaxf(m_hi, mx_hi);       // finite: key 0 is visible to every query and lies in tile 0
+            const float c_lo = exp2f(m_lo - n_lo), c_hi = exp2f(m_hi - n_hi);
+            m_lo = n_lo; m_hi = n_hi;
+            float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+            for (int nb = 0; nb < 4; ++nb) {
+                s[nb][0] = exp2f(s[nb][0] - n_lo); s[nb][1] = exp2f(s[nb][1] - n_lo); s[nb][2] = exp2f(s[nb][2] - n_hi); s[nb][3] = exp2f(s[nb][3] - n_hi);
+                sum_lo += s[nb][0] + s[nb][1]; sum_hi += s[nb][2] + s[nb][3];
+            }
+            l_lo = l_lo * c_lo + sum_lo; l_hi = l_hi * c_hi + sum_hi;
+#pragma unroll
+            for (int i = 0; i < NVB; ++i) { o[i][0] *= c_lo; o[i][1] *= c_lo; o[i][2] *= c_hi; o[i][3] *= c_hi; }
+            const uint32_t va = smem_u32(Kb + (((lane >> 3) & 1) * 8 + (lane & 7)) * EP + vbase + (lane >> 4) * 8);
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+                const uint32_t a0 = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]), a1 = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
+                const uint32_t a2 = pack_bf16x2(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = pack_bf16x2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int np = 0; np < NVB / 2; ++np) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(va + kk * 16 * EP * 2 + np * 32, b0, b1, b2, b3);
+                    mma_bf16_16816(o[2 * np], a0, a1, a2, a3, b0, b1); mma_bf16_16816(o[2 * np + 1], a0, a1, a2, a3, b2, b3);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (!active) return;
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    const float i_lo = 1.0f / l_lo, i_hi = 1.0f / l_hi;
+    const int q_lo = 16 * warp + (lane >> 2), q_hi = q_lo + 8;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int qi = half ? q_hi : q_lo;
+        if (qi >= nq) continue;
+        const int row = row0 + (q0 + qi) / H, h = (q0 + qi) % H; const float inv = half ? i_hi : i_lo;
+        __nv_bfloat16* dst = lat_out + ((long long)row * H + h) * R + vbase + (lane & 3) * 2;
+#pragma unroll
+        for (int nb = 0; nb < NVB; ++nb) *reinterpret_cast<uint32_t*>(dst + nb * 8) = pack_bf16x2(o[nb][half * 2] * inv, o[nb][half * 2 + 1] * inv);
     }
 }
 
@@ -531,6 +656,29 @@ cudaError_t hy_mla_attention(bool f32, const HyLatentAttn& a, const float* q_abs
     const size_t smem = (size_t)(a.kv_rank + a.rot_dim + 4 * a.kv_rank + 8) * 4;
     return f32 ? launch_plain(hy_mla_attention_kernel<float>, dim3(r.T, a.heads), dim3(128), smem, s, a, q_abs, (const float*)cache, (float*)lat_out, r)
                : launch_plain(hy_mla_attention_kernel<bf>, dim3(r.T, a.heads), dim3(128), smem, s, a, q_abs, (const bf*)cache, (bf*)lat_out, r);
+}
+static int mla_mma_nvb(const HyLatentAttn& a) {
+    const int E = a.kv_rank + a.rot_dim;
+    if (E % 16 != 0 || a.kv_rank % 64 != 0) return 0;
+    const int nvb = a.kv_rank % 256 == 0 ? 32 : (a.kv_rank % 128 == 0 ? 16 : 8);
+    const size_t smem = (size_t)(MLA_MQ + 2 * MLA_KT) * (E + 8) * 2 + MLA_MQ * 4;
+    return smem <= 200 * 1024 ? nvb : 0;
+}
+bool hy_mla_mma_supported(const HyLatentAttn& a) { return mla_mma_nvb(a) != 0; }
+cudaError_t hy_mla_attention_mma(const HyLatentAttn& a, const float* q_abs, const void* cache, void* lat_out, const HyRows& r, const int32_t* tile_seq,
+                                 const int32_t* tile_q0, int n_tiles, cudaStream_t s) {
+    const int nvb = mla_mma_nvb(a), E = a.kv_rank + a.rot_dim;
+    if (!nvb) return cudaErrorInvalidValue;
+    const size_t smem = (size_t)(MLA_MQ + 2 * MLA_KT) * (E + 8) * 2 + MLA_MQ * 4;
+    dim3 grid(n_tiles, a.kv_rank / (nvb * 8));
+    static bool done[3][16] = {};
+    cudaError_t e;
+    if (nvb == 32) { if ((e = ensure_dynamic_smem(hy_mla_attention_mma_kernel<32>, (int)smem, done[0])) != cudaSuccess) return e;
+        return launch_plain(hy_mla_attention_mma_kernel<32>, grid, dim3(128), smem, s, a, q_abs, (const bf*)cache, (bf*)lat_out, r, tile_seq, tile_q0); }
+    if (nvb == 16) { if ((e = ensure_dynamic_smem(hy_mla_attention_mma_kernel<16>, (int)smem, done[1])) != cudaSuccess) return e;
+        return launch_plain(hy_mla_attention_mma_kernel<16>, grid, dim3(128), smem, s, a, q_abs, (const bf*)cache, (bf*)lat_out, r, tile_seq, tile_q0); }
+    if ((e = ensure_dynamic_smem(hy_mla_attention_mma_kernel<8>, (int)smem, done[2])) != cudaSuccess) return e;
+    return launch_plain(hy_mla_attention_mma_kernel<8>, grid, dim3(128), smem, s, a, q_abs, (const bf*)cache, (bf*)lat_out, r, tile_seq, tile_q0);
 }
 cudaError_t hy_conv_silu(bool f32, const void* in, int ld_in, int C, const float* w, const float* bias, int taps, void* out, int ld_out, const void* tails, const HyRows& r,
                          cudaStream_t s) {

@@ -46,6 +46,13 @@ cudaError_t hy_mla_prep(bool f32, const HyLatentAttn& a, const void* q, int ldq,
 // lat_out[t, h, :rank] = sum_j softmax_j(scale * q_abs[t,h] . cache[j]) cache[j][:rank]
 cudaError_t hy_mla_attention(bool f32, const HyLatentAttn& a, const float* q_abs, const void* cache, void* lat_out, const HyRows& r, cudaStream_t s);
 
+// the same on the tensor cores (bf16 only; sizes: kv_rank a multiple of 64, kv_rank + rot_dim of 16).  A tile = 64 consecutive (row, head)
+// pairs of one sequence starting at pair tile_q0 of sequence tile_seq; the host lists the tiles of a step.
+constexpr int HY_MLA_TILE_QUERIES = 64;
+bool hy_mla_mma_supported(const HyLatentAttn& a);
+cudaError_t hy_mla_attention_mma(const HyLatentAttn& a, const float* q_abs, const void* cache, void* lat_out, const HyRows& r, const int32_t* tile_seq,
+                                 const int32_t* tile_q0, int n_tiles, cudaStream_t s);
+
 // y = silu(causal conv over time of `in` per channel (+ bias)); inputs before a sequence's first row of this step come from its tail
 // (the last taps-1 inputs of earlier steps; zeros at the start of a sequence).  hy_conv_tails then stores the new tails.
 cudaError_t hy_conv_silu(bool f32, const void* in, int ld_in, int C, const float* w, const float* bias, int taps, void* out, int ld_out,

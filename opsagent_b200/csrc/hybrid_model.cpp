@@ -279,6 +279,7 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
         }
     }
     meta_cap_words_ = 4 * MR + (size_t)MS_ + (size_t)opt.max_batch * (max_pages_per_seq + 8) + 64;
+    for (const HyLayer& l : hc_.layers) if (l.type == HY_LATENT_ATTENTION) meta_cap_words_ += 2 * (MR * l.heads / HY_MLA_TILE_QUERIES + (size_t)opt.max_batch + 8);
     for (int i = 0; i < 2; ++i) {
         cuda_check(cudaMallocHost(&h_meta_buf_[i], meta_cap_words_ * 4), "cudaMallocHost meta");
         cuda_check(cudaEventCreateWithFlags(&meta_ev_[i], cudaEventDisableTiming), "cudaEventCreate meta");
@@ -350,6 +351,12 @@ void HybridModel::moe(const LayerW& w, const HyLayer& l, const HyRows& r) {
     cuda_check(hy_moe_down(f32_, act_, w.down, W, w.ffp, idx_, wgt_, m.top, x_, T, stream), "experts down");
 }
 
+const char* HybridModel::kt_name(int id) const {
+    static const char* n[16] = {"h2d+embed", "layer_norm", "in_proj_gemm", "latent_absorb+up_gemm", "latent_cache_write", "latent_attention", "conv", "recurrence_prep",
+                                "recurrence", "gated_norm", "low_rank_gemm", "out_proj_gemm", "router", "experts", "loop_in", "head+argmax"};
+    return n[id & 15];
+}
+
 void HybridModel::forward(const StepInput& in, float* logits_out) {
     const int T = (int)in.tokens.size(), S = in.n_seqs, NS = (int)in.sample_rows.size(), W = hc_.width, V = hc_.vocab;
     if (T <= 0 || T > MR_ || NS > MS_ || S <= 0 || S > opt.max_batch) throw std::runtime_error("forward: bad batch size");
@@ -373,6 +380,22 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
     const size_t o_tok = put(in.tokens.data(), T), o_pos = put(in.positions.data(), T), o_slot = put(in.slots.data(), T), o_samp = put(in.sample_rows.data(), NS);
     const size_t o_bt = put(in.block_tables.data(), in.block_tables.size()), o_rs = put(row_seq_.data(), T), o_r0 = put(in.seq_row0.data(), S + 1);
     const size_t o_p0 = put(seq_pos0_.data(), S), o_st = put(in.state_slots.data(), S);
+    // tensor-core attention: tiles of 64 consecutive (row, head) pairs of one sequence, listed once per distinct head count
+    struct TileList { int heads; size_t o_seq, o_q0; int n; };
+    std::vector<TileList> tile_lists;
+    if (!f32_ && opt.hy_tensor_core)
+        for (const HyLayer& l : hc_.layers) {
+            if (l.type != HY_LATENT_ATTENTION || !hy_mla_mma_supported(HyLatentAttn{l.heads, l.dim, l.rot_dim, l.vdim, l.kv_rank, l.rot_dims, l.scale})) continue;
+            bool have = false; for (const TileList& tl : tile_lists) have |= tl.heads == l.heads;
+            if (have) continue;
+            tile_seq_.clear(); tile_q0_.clear();
+            for (int sq = 0; sq < S; ++sq) {
+                const int nq = (in.seq_row0[sq + 1] - in.seq_row0[sq]) * l.heads;
+                for (int q0 = 0; q0 < nq; q0 += HY_MLA_TILE_QUERIES) { tile_seq_.push_back(sq); tile_q0_.push_back(q0); }
+            }
+            TileList tl; tl.heads = l.heads; tl.n = (int)tile_seq_.size(); tl.o_seq = put(tile_seq_.data(), tile_seq_.size()); tl.o_q0 = put(tile_q0_.data(), tile_q0_.size());
+            tile_lists.push_back(tl);
+        }
     cuda_check(cudaMemcpyAsync(d_meta_, hm, wd * 4, cudaMemcpyHostToDevice, stream), "meta H2D");
     cuda_check(cudaEventRecord(meta_ev_[meta_idx_], stream), "meta event");
     h2d_bytes += wd * 4;
@@ -382,49 +405,60 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
     if (dbg_layers && !capture_layers) capture_layers = &dbg_buf;
     if (capture_layers) capture_layers->clear();
 
-    cuda_check(hy_embed(f32_, d_meta_ + o_tok, embed_, x_, x0_, T, W, V, stream), "embed");
+    size_t ek = 0;
+    if (profile_all) {
+        const size_t need = hc_.runs.size() * 16 + 16;
+        if (ev_all.size() < need) { size_t o = ev_all.size(); ev_all.resize(need); for (size_t i = o; i < need; ++i) cudaEventCreate(&ev_all[i]); }
+        ev_ids.assign(ev_all.size(), 0);
+        cudaEventRecord(ev_all[ek++], stream);
+    }
+    auto MARK = [&](int id) { if (profile_all && ek < ev_all.size()) { ev_ids[ek] = id; cudaEventRecord(ev_all[ek++], stream); } };
+    cuda_check(hy_embed(f32_, d_meta_ + o_tok, embed_, x_, x0_, T, W, V, stream), "embed"); MARK(0);
     auto at = [&](void* base, size_t elems) -> void* { return reinterpret_cast<char*>(base) + elems * es_; };
     for (const HyRun& run : hc_.runs) {
         const HyLayer& l = hc_.layers[run.layer]; const LayerW& w = lw_[run.layer];
         if (run.first_of_pass) {         // re-injection: x <- W_in [x ; x0] + step[pass]
             cuda_check(hy_concat(f32_, x_, x0_, cat_, T, W, stream), "concat");
-            gemm(HY_STORE_F32, cat_, 2 * W, loop_in_, x_, W, T, loop_step_ + (size_t)run.pass * W, 1.f);
+            gemm(HY_STORE_F32, cat_, 2 * W, loop_in_, x_, W, T, loop_step_ + (size_t)run.pass * W, 1.f); MARK(14);
         }
-        cuda_check(hy_layernorm(f32_, x_, nullptr, w.norm1, h_, Wld_, T, W, hc_.eps, stream), "layer norm");
-        gemm(HY_STORE, h_, Wld_, w.in, proj_, ld_proj_, T, nullptr, 1.f);
+        cuda_check(hy_layernorm(f32_, x_, nullptr, w.norm1, h_, Wld_, T, W, hc_.eps, stream), "layer norm"); MARK(1);
+        gemm(HY_STORE, h_, Wld_, w.in, proj_, ld_proj_, T, nullptr, 1.f); MARK(2);
         if (l.type == HY_LATENT_ATTENTION) {
             const HyLatentAttn a{l.heads, l.dim, l.rot_dim, l.vdim, l.kv_rank, l.rot_dims, l.scale};
             const int E = l.kv_rank + l.rot_dim;
             // absorbed queries: q_abs[t, h, :rank] = W_uk[h]^T q_unrotated[t, h]
             cuda_check(hy_gemm(f32_, HY_STORE_F32, at(proj_, w.off_a), ld_proj_, w.uk_t, l.dim, q_abs_, l.heads * E, T, l.kv_rank, l.dim, nullptr, 1.f, l.heads,
-                               l.dim + l.rot_dim, (long long)l.kv_rank * l.dim, E, stream), "query absorption");
+                               l.dim + l.rot_dim, (long long)l.kv_rank * l.dim, E, stream), "query absorption"); MARK(3);
             cuda_check(hy_mla_prep(f32_, a, at(proj_, w.off_a), ld_proj_, at(proj_, w.off_b), ld_proj_, w.dkv_norm, hc_.eps, ropes_[w.rope].cos, ropes_[w.rope].sin,
-                                   caches_[run.cache_idx], q_abs_, r, stream), "latent cache write");
-            cuda_check(hy_mla_attention(f32_, a, q_abs_, caches_[run.cache_idx], lat_, r, stream), "latent attention");
+                                   caches_[run.cache_idx], q_abs_, r, stream), "latent cache write"); MARK(4);
+            const TileList* tl = nullptr; for (const TileList& t : tile_lists) if (t.heads == l.heads && hy_mla_mma_supported(a)) tl = &t;
+            if (tl) cuda_check(hy_mla_attention_mma(a, q_abs_, caches_[run.cache_idx], lat_, r, d_meta_ + tl->o_seq, d_meta_ + tl->o_q0, tl->n, stream), "latent attention (mma)");
+            else cuda_check(hy_mla_attention(f32_, a, q_abs_, caches_[run.cache_idx], lat_, r, stream), "latent attention");
+            MARK(5);
             cuda_check(hy_gemm(f32_, HY_STORE, lat_, l.heads * l.kv_rank, w.uv, l.kv_rank, mix_, ld_mix_, T, l.vdim, l.kv_rank, nullptr, 1.f, l.heads, l.kv_rank,
-                               (long long)l.vdim * l.kv_rank, l.vdim, stream), "value up-projection");
+                               (long long)l.vdim * l.kv_rank, l.vdim, stream), "value up-projection"); MARK(3);
         } else if (l.type == HY_CHANNEL_DELTA) {
             const HyDelta d{l.heads, l.kv_heads, l.dim, l.vdim};
             cuda_check(hy_conv_silu(f32_, at(proj_, w.off_a), ld_proj_, w.conv_ch, w.conv_w, nullptr, l.conv, conv_, ld_conv_, tails_[run.state_idx], r, stream), "conv");
-            cuda_check(hy_conv_tails(f32_, at(proj_, w.off_a), ld_proj_, w.conv_ch, l.conv, tails_[run.state_idx], r, stream), "conv tails");
+            cuda_check(hy_conv_tails(f32_, at(proj_, w.off_a), ld_proj_, w.conv_ch, l.conv, tails_[run.state_idx], r, stream), "conv tails"); MARK(6);
             const int off_g = up8(l.heads * l.dim);
             gemm(HY_STORE, at(proj_, w.off_c), ld_proj_, w.a2, p2_, ld_p2_, T, nullptr, 1.f);
-            gemm(HY_STORE, at(proj_, w.off_d), ld_proj_, w.g2, at(p2_, off_g), ld_p2_, T, nullptr, 1.f);
-            cuda_check(hy_delta_prep(f32_, d, conv_, ld_conv_, at(proj_, w.off_b), ld_proj_, p2_, ld_p2_, w.A_log, w.dt_bias, qq_, kk_, vv_, dec_, beta_, T, stream), "delta prep");
-            cuda_check(hy_recurrence(true, qq_, kk_, vv_, dec_, beta_, rec_, states_[run.state_idx], l.heads, l.kv_heads, l.dim, l.vdim, r, stream), "delta rule");
-            cuda_check(hy_gated_norm(f32_, rec_, l.heads * l.vdim, l.vdim, w.norm_w, l.vdim, at(p2_, off_g), ld_p2_, 0, 0, nullptr, 1, nullptr, 0, mix_, ld_mix_, hc_.eps, T, stream), "gated norm");
+            gemm(HY_STORE, at(proj_, w.off_d), ld_proj_, w.g2, at(p2_, off_g), ld_p2_, T, nullptr, 1.f); MARK(10);
+            cuda_check(hy_delta_prep(f32_, d, conv_, ld_conv_, at(proj_, w.off_b), ld_proj_, p2_, ld_p2_, w.A_log, w.dt_bias, qq_, kk_, vv_, dec_, beta_, T, stream), "delta prep"); MARK(7);
+            cuda_check(hy_recurrence(true, qq_, kk_, vv_, dec_, beta_, rec_, states_[run.state_idx], l.heads, l.kv_heads, l.dim, l.vdim, r, stream), "delta rule"); MARK(8);
+            cuda_check(hy_gated_norm(f32_, rec_, l.heads * l.vdim, l.vdim, w.norm_w, l.vdim, at(p2_, off_g), ld_p2_, 0, 0, nullptr, 1, nullptr, 0, mix_, ld_mix_, hc_.eps, T, stream), "gated norm"); MARK(9);
         } else {
             const HyMamba m{l.heads, l.vdim, l.state, l.groups};
             const int inner = l.heads * l.vdim;
             cuda_check(hy_conv_silu(f32_, at(proj_, w.off_b), ld_proj_, w.conv_ch, w.conv_w, w.conv_b, l.conv, conv_, ld_conv_, tails_[run.state_idx], r, stream), "conv");
-            cuda_check(hy_conv_tails(f32_, at(proj_, w.off_b), ld_proj_, w.conv_ch, l.conv, tails_[run.state_idx], r, stream), "conv tails");
-            cuda_check(hy_mamba_prep(f32_, m, conv_, ld_conv_, at(proj_, w.off_c), ld_proj_, w.A_log, w.dt_bias, qq_, kk_, vv_, dec_, T, stream), "mamba prep");
-            cuda_check(hy_recurrence(false, qq_, kk_, vv_, dec_, nullptr, rec_, states_[run.state_idx], l.heads, l.groups, l.state, l.vdim, r, stream), "state-space recurrence");
+            cuda_check(hy_conv_tails(f32_, at(proj_, w.off_b), ld_proj_, w.conv_ch, l.conv, tails_[run.state_idx], r, stream), "conv tails"); MARK(6);
+            cuda_check(hy_mamba_prep(f32_, m, conv_, ld_conv_, at(proj_, w.off_c), ld_proj_, w.A_log, w.dt_bias, qq_, kk_, vv_, dec_, T, stream), "mamba prep"); MARK(7);
+            cuda_check(hy_recurrence(false, qq_, kk_, vv_, dec_, nullptr, rec_, states_[run.state_idx], l.heads, l.groups, l.state, l.vdim, r, stream), "state-space recurrence"); MARK(8);
             cuda_check(hy_gated_norm(f32_, rec_, inner, inner / l.norm_groups, w.norm_w, inner, at(proj_, w.off_a), ld_proj_, 1, 1, w.D, l.vdim, conv_, ld_conv_, mix_, ld_mix_,
-                                     hc_.eps, T, stream), "gated norm");
+                                     hc_.eps, T, stream), "gated norm"); MARK(9);
         }
-        gemm(HY_ACC_F32, mix_, ld_mix_, w.o, x_, W, T, nullptr, 1.f);
-        if (l.moe.present) moe(w, l, r);
+        gemm(HY_ACC_F32, mix_, ld_mix_, w.o, x_, W, T, nullptr, 1.f); MARK(11);
+        if (l.moe.present) { moe(w, l, r); MARK(13); }
         if (capture_layers) {
             cuda_check(cudaStreamSynchronize(stream), "capture sync");
             const size_t n0 = capture_layers->size(); capture_layers->resize(n0 + (size_t)T * W);
@@ -441,7 +475,11 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
         gemm(HY_STORE_F32, hs_, Wld_, head_, lg, V, NS, nullptr, hc_.logit_scale);
         cuda_check(hy_argmax_rows(lg, NS, V, d_out_ids_, stream), "argmax");
         cuda_check(cudaMemcpyAsync(h_out_ids, d_out_ids_, (size_t)NS * 4, cudaMemcpyDeviceToHost, stream), "ids D2H");
-        d2h_bytes += (size_t)NS * 4;
+        d2h_bytes += (size_t)NS * 4; MARK(15);
+    }
+    if (profile_all) {
+        cuda_check(cudaStreamSynchronize(stream), "profile sync");
+        for (size_t i = 1; i < ek; ++i) { float ms = 0; cudaEventElapsedTime(&ms, ev_all[i - 1], ev_all[i]); kt_ms[ev_ids[i] & 15] += ms; kt_n[ev_ids[i] & 15]++; }
     }
 }
 

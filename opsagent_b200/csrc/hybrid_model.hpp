@@ -17,6 +17,7 @@ public:
     HybridModel(const ModelConfig& cfg, const EngineOptions& opt);
     ~HybridModel() override;
     void forward(const StepInput& in, float* logits_out) override;
+    const char* kt_name(int id) const override;
     // debug: copy of the residual stream after every layer execution of the NEXT forward ([runs, T, width] fp32, host); empty = off
     std::vector<float>* capture_layers = nullptr;
 
@@ -64,7 +65,7 @@ private:
     int32_t *idx_ = nullptr, *d_out_ids_ = nullptr, *tile_expert_ = nullptr, *row_src_ = nullptr, *n_tiles_ = nullptr, *dst_of_ = nullptr; int max_tiles_ = 0;
     int32_t* h_meta_buf_[2] = {nullptr, nullptr}; cudaEvent_t meta_ev_[2] = {nullptr, nullptr}; int meta_idx_ = 0;
     int32_t* d_meta_ = nullptr; size_t meta_cap_words_ = 0;
-    std::vector<int32_t> row_seq_, seq_pos0_;
+    std::vector<int32_t> row_seq_, seq_pos0_, tile_seq_, tile_q0_;
 };
 
 }  // namespace oa

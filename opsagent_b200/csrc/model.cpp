@@ -308,7 +308,7 @@ DeviceModel::~DeviceModel() {
     if (stream) cudaStreamDestroy(stream);
 }
 
-const char* ModelBase::kt_name(int id) {
+const char* ModelBase::kt_name(int id) const {
     static const char* n[16] = {"h2d+embed", "rmsnorm", "qkv_gemm", "rope_kv", "attention", "attn_merge", "o_gemm", "resid_rmsnorm", "gate_up_gemm",
                                 "swiglu", "down_gemm", "gather+norm", "lm_head", "argmax+d2h", "", ""};
     return n[id & 15];

@@ -1,0 +1,72 @@
+"""Throughput of the Ratasun hybrid family beside the closest Llama-family model of equal width, depth and active feed-forward size
+(`bench.py --arch ratasun`).  Random weights (seeded on load), synthetic token ids; prefill = real chunked prefill of batch x (ctx-1) tokens,
+decode = steps of the whole batch, both timed with CUDA events inside the engine (oa_bench_decode).  With --breakdown the per-kernel-class
+device times come from the engine's in-situ event timing (OA_PROFILE_ALL), one pass for prefill and one for decode."""
+from __future__ import annotations
+
+import json
+import os
+import tempfile
+
+
+def sizes(name: str) -> dict:
+    if name == "small":
+        att = {"heads": 8, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256, "scale": 96 ** -0.5, "rot": {"base": 10000.0, "dims": 32}}
+        dl = {"heads": 8, "kv_heads": 4, "dim": 64, "vdim": 128, "conv": 4}
+        mb = {"heads": 16, "vdim": 64, "state": 64, "groups": 2, "norm_groups": 1, "conv": 4}
+        moe = {"kind": "moe", "expert": {"ff": 512}, "router": {"experts": 16, "top": 4, "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
+        width, vocab = 1024, 32000
+    else:
+        att = {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64}}
+        dl = {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "conv": 4}
+        mb = {"heads": 32, "vdim": 64, "state": 128, "groups": 4, "norm_groups": 1, "conv": 4}
+        moe = {"kind": "moe", "expert": {"ff": 1024}, "router": {"experts": 32, "top": 4, "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
+        width, vocab = 2048, 32000
+    layers = [{"type": t, "mixer": m, "mlp": moe} for t, m in (("latent_attention", att), ("channel_delta", dl), ("mamba2", mb), ("latent_attention", att))]
+    cfg = {"architecture": "Ratasun", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "logit_scale": 1.0, "layers": layers,
+           "loop": {"start": 1, "stop": 3, "times": 2}}
+    runs = 6
+    ff_active = moe["router"]["top"] * moe["expert"]["ff"]
+    hd = 64 if width == 1024 else 128
+    llama = {"model": "custom", "hidden": width, "n_layers": runs, "n_heads": width // hd, "n_kv_heads": max(1, width // hd // 4), "head_dim": hd, "ffn": ff_active, "vocab": vocab}
+    return {"hybrid": cfg, "llama": llama, "runs": runs}
+
+
+def one(engine_cfg: dict, batch: int, ctx: int, steps: int, warmup: int, breakdown: bool) -> dict:
+    from .engine import Engine
+    out = {}
+    with Engine(engine_cfg) as eng:
+        r = eng.bench_decode(batch, ctx, steps, warmup)
+        out["prefill_tok_s"] = batch * (ctx - 1) / (r["prefill_ms"] / 1e3)
+        out["prefill_ms"] = r["prefill_ms"]
+        out["decode_tok_s"] = batch / (r["ms_per_step"] / 1e3)
+        out["decode_ms_per_step"] = r["ms_per_step"]
+        out["launches_per_step"] = r["launches_per_step"]
+        out["weight_bytes"] = eng.stats()["weight_bytes"]
+        if breakdown:
+            os.environ["OA_PROFILE_ALL"] = "1"
+            eng.kernel_times(reset=True)
+            eng.bench_decode(batch, ctx, 4, 1)
+            out["decode_kernel_ms"] = {k: round(v[0] / 4, 4) for k, v in eng.kernel_times(reset=True).items() if v[1]}
+            os.environ["OA_PROFILE_PREFILL"] = "1"
+            eng.bench_decode(batch, ctx, 1, 0)
+            out["prefill_kernel_ms"] = {k: round(v[0], 3) for k, v in eng.kernel_times(reset=True).items() if v[1]}
+            del os.environ["OA_PROFILE_PREFILL"], os.environ["OA_PROFILE_ALL"]
+    return out
+
+
+def run(args) -> None:
+    res = {"metric": "hybrid_vs_llama_throughput", "unit": "tokens/s", "data": "synthetic", "dtype": "bf16", "cases": []}
+    for name in args.arch_sizes.split(","):
+        sz = sizes(name)
+        batch, ctx = args.arch_batch, args.arch_ctx
+        pages = batch * ((ctx + args.steps + args.warmup + 64) // 64 + 1)
+        common = {"num_pages": pages, "max_batch": batch, "max_seq_len": (ctx + args.steps + args.warmup + 127) // 64 * 64, "max_step_tokens": 8192, "prefix_cache": 0}
+        with tempfile.TemporaryDirectory() as d:
+            with open(os.path.join(d, "config.json"), "w") as f:
+                json.dump(sz["hybrid"], f)
+            hy = one(dict(common, model_dir=d, **json.loads(args.engine_extra)), batch, ctx, args.steps, args.warmup, args.breakdown)
+        ll = one(dict(common, **sz["llama"]), batch, ctx, args.steps, args.warmup, args.breakdown)
+        res["cases"].append({"size": name, "batch": batch, "ctx": ctx, "layer_runs": sz["runs"], "ratasun": hy, "llama_equal_size": ll,
+                             "prefill_ratio": hy["prefill_tok_s"] / ll["prefill_tok_s"], "decode_ratio": hy["decode_tok_s"] / ll["decode_tok_s"]})
+    print(json.dumps(res))
