@@ -876,7 +876,7 @@ int oa_debug_kernel_times(oa_engine* h, char* buf, size_t n, int32_t reset) {
     if (!h || !buf) return fail(OA_ERR_BAD_REQUEST, "null argument");
     ModelBase& m = h->e->model();
     std::string s = "{";
-    for (int i = 0; i < 16; ++i) {
+    for (int i = 0; i < 32; ++i) {
         if (!m.kt_name(i)[0]) continue;
         char t[128]; std::snprintf(t, sizeof t, "%s\"%s\": [%.4f, %ld]", s.size() > 1 ? ", " : "", m.kt_name(i), m.kt_ms[i], m.kt_n[i]); s += t;
         if (reset) { m.kt_ms[i] = 0; m.kt_n[i] = 0; }

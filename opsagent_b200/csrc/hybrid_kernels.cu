@@ -35,6 +35,10 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return t;
 }
 
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
+}
+
 template <typename... KArgs, typename... Args>
 cudaError_t launch_plain(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
     count_launch();
@@ -194,9 +198,6 @@ __global__ void __launch_bounds__(128) hy_mla_attention_kernel(HyLatentAttn a, c
 // registers, with the mask applied per query position.  A CTA accumulates NVB * 8 of the latent's channels (blockIdx.y picks which).
 // ---------------------------------------------------------------------------------------------------------------------------------
 constexpr int MLA_MQ = 64, MLA_KT = 32;
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
-}
 template <int NVB>
 __global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn a, const float* __restrict__ q_abs, const __nv_bfloat16* __restrict__ cache,
                                                                    __nv_bfloat16* __restrict__ lat_out, HyRows r, const int32_t* __restrict__ tile_seq,
@@ -416,6 +417,101 @@ __global__ void __launch_bounds__(REC_COLS) hy_recurrence_kernel(const float* qq
     if (ok) for (int d = 0; d < D; ++d) st[(long long)d * VD + col] = S[d * REC_COLS + j];
 }
 
+// Register-resident variant for dim <= 8 * DP (dim and vdim multiples of 4): a thread owns two state columns (value channels), each split
+// over 8 lanes that hold DP of its rows in registers; the dot products of a step meet through three shuffles.  The per-token operands
+// (q, k, decay slices, 32 values, the scalar) arrive through an 8-deep cp.async ring in shared memory — every copying thread keeps its own
+// source pointer and advances it by a constant per token — so a step never waits on global memory and spends few instructions outside the
+// multiply-adds.  32 columns per 128-thread CTA: even one decoding sequence spreads over heads x vdim / 32 CTAs.  The order of every sum is
+// fixed (lane-local rows ascending in two interleaved chains, then the shuffle tree), whatever else the step holds.
+constexpr int REC_STAGES = 8, REC_CTA_COLS = 32;
+template <bool DELTA, int DP>
+__global__ void __launch_bounds__(128) hy_recurrence_reg_kernel(const float* __restrict__ qq, const float* __restrict__ kk, const float* __restrict__ vv,
+                                                                const float* __restrict__ dec, const float* __restrict__ beta, float* __restrict__ out,
+                                                                float* __restrict__ state, int H, int QH, int D, int VD, HyRows r) {
+    extern __shared__ __align__(16) float rec_ring[];
+    constexpr int DPAD = 8 * DP;                    // rows padded to the lanes' slices: pad rows hold q = k = 0, decay 1, so they stay zero
+    constexpr int stride = 3 * DPAD + 36;           // floats per stage: q[DPAD] k[DPAD] g[DPAD] v[32] scalar (padded to 16 bytes)
+    const int tid = threadIdx.x, part = tid & 7, cl = tid >> 3, col = blockIdx.z * REC_CTA_COLS + 2 * cl;
+    const int seq = blockIdx.x, h = blockIdx.y;
+    const bool ok0 = col < VD, ok1 = col + 1 < VD;
+    const int row0 = r.seq_row0[seq], len = r.seq_row0[seq + 1] - row0, pos0 = r.seq_pos0[seq], qh = h / (H / QH), d0 = part * DP;
+    float* st = state + ((long long)r.seq_state[seq] * H + h) * D * VD;
+    float S0[DP], S1[DP];
+#pragma unroll
+    for (int i = 0; i < DP; ++i) {
+        const bool in = pos0 > 0 && d0 + i < D;
+        S0[i] = (ok0 && in) ? st[(long long)(d0 + i) * VD + col] : 0.f; S1[i] = (ok1 && in) ? st[(long long)(d0 + i) * VD + col + 1] : 0.f;
+    }
+    for (int i = tid; i < REC_STAGES * stride; i += 128) { const int w = i % stride; rec_ring[i] = (w >= 2 * DPAD && w < 3 * DPAD) ? 1.f : 0.f; }
+    __syncthreads();
+    // this thread's copy role: one 16-byte piece (or the 4-byte scalar) per token, source advancing by `step` floats per token
+    const int dq = D / 4, n_vec = (DELTA ? 3 : 2) * dq;
+    const float* src = nullptr; int dst = 0, bytes = 0; long long step = 0;
+    if (tid < n_vec) {
+        const int which = tid / dq, c = tid - which * dq;
+        src = (which == 0 ? qq + ((long long)row0 * QH + qh) * D : which == 1 ? kk + ((long long)row0 * QH + qh) * D : dec + ((long long)row0 * H + h) * D) + c * 4;
+        step = which == 2 ? (long long)H * D : (long long)QH * D; dst = which * DPAD + c * 4; bytes = 16;
+    } else if (tid >= 96 && tid < 104) {
+        const int c = tid - 96;
+        if (blockIdx.z * REC_CTA_COLS + c * 4 < VD) { src = vv + ((long long)row0 * H + h) * VD + blockIdx.z * REC_CTA_COLS + c * 4; step = (long long)H * VD; dst = 3 * DPAD + c * 4; bytes = 16; }
+    } else if (tid == 104) {
+        src = (DELTA ? beta : dec) + (long long)row0 * H + h; step = H; dst = 3 * DPAD + 32; bytes = 4;
+    }
+    int issued = 0;
+    auto issue = [&]() {                             // next token of the sequence's rows -> ring slot issued % REC_STAGES
+        if (issued < len && bytes) {
+            float* d = rec_ring + (issued % REC_STAGES) * stride + dst;
+            if (bytes == 16) cp_async16(d, src);
+            else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(d)), "l"(src) : "memory");
+            src += step;
+        }
+        ++issued;
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    for (int i = 0; i < REC_STAGES - 1; ++i) issue();
+    float* op = out + ((long long)row0 * H + h) * VD + col;
+    for (int i = 0; i < len; ++i) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(REC_STAGES - 2) : "memory");
+        __syncthreads();                             // token i has landed for everybody; slot (i - 1) % STAGES is free again
+        issue();
+        const float* slot = rec_ring + (i % REC_STAGES) * stride;
+        const float2 v = *reinterpret_cast<const float2*>(slot + 3 * DPAD + 2 * cl); const float sc = slot[3 * DPAD + 32];
+        float q[DP], k[DP];
+#pragma unroll
+        for (int j = 0; j < DP; j += 4) {
+            const float4 q4 = *reinterpret_cast<const float4*>(slot + d0 + j), k4 = *reinterpret_cast<const float4*>(slot + DPAD + d0 + j);
+            q[j] = q4.x; q[j + 1] = q4.y; q[j + 2] = q4.z; q[j + 3] = q4.w; k[j] = k4.x; k[j + 1] = k4.y; k[j + 2] = k4.z; k[j + 3] = k4.w;
+        }
+        float o0 = 0.f, o1 = 0.f;
+        if (DELTA) {
+            float dot0 = 0.f, dot1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < DP; j += 4) {
+                const float4 g4 = *reinterpret_cast<const float4*>(slot + 2 * DPAD + d0 + j);
+                S0[j] *= g4.x; S0[j + 1] *= g4.y; S0[j + 2] *= g4.z; S0[j + 3] *= g4.w; S1[j] *= g4.x; S1[j + 1] *= g4.y; S1[j + 2] *= g4.z; S1[j + 3] *= g4.w;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) { dot0 = fmaf(S0[j + u], k[j + u], dot0); dot1 = fmaf(S1[j + u], k[j + u], dot1); }
+            }
+            dot0 += __shfl_xor_sync(0xffffffffu, dot0, 1); dot1 += __shfl_xor_sync(0xffffffffu, dot1, 1);
+            dot0 += __shfl_xor_sync(0xffffffffu, dot0, 2); dot1 += __shfl_xor_sync(0xffffffffu, dot1, 2);
+            dot0 += __shfl_xor_sync(0xffffffffu, dot0, 4); dot1 += __shfl_xor_sync(0xffffffffu, dot1, 4);
+            const float u0 = sc * (v.x - dot0), u1 = sc * (v.y - dot1);
+#pragma unroll
+            for (int j = 0; j < DP; ++j) { S0[j] = fmaf(k[j], u0, S0[j]); S1[j] = fmaf(k[j], u1, S1[j]); o0 = fmaf(S0[j], q[j], o0); o1 = fmaf(S1[j], q[j], o1); }
+        } else {
+#pragma unroll
+            for (int j = 0; j < DP; ++j) { S0[j] = fmaf(k[j], v.x, S0[j] * sc); S1[j] = fmaf(k[j], v.y, S1[j] * sc); o0 = fmaf(S0[j], q[j], o0); o1 = fmaf(S1[j], q[j], o1); }
+        }
+        o0 += __shfl_xor_sync(0xffffffffu, o0, 1); o1 += __shfl_xor_sync(0xffffffffu, o1, 1);
+        o0 += __shfl_xor_sync(0xffffffffu, o0, 2); o1 += __shfl_xor_sync(0xffffffffu, o1, 2);
+        o0 += __shfl_xor_sync(0xffffffffu, o0, 4); o1 += __shfl_xor_sync(0xffffffffu, o1, 4);
+        if (part == 0) { if (ok1) *reinterpret_cast<float2*>(op) = make_float2(o0, o1); else if (ok0) *op = o0; }
+        op += (long long)H * VD;
+    }
+#pragma unroll
+    for (int i = 0; i < DP; ++i) if (d0 + i < D) { if (ok0) st[(long long)(d0 + i) * VD + col] = S0[i]; if (ok1) st[(long long)(d0 + i) * VD + col + 1] = S1[i]; }
+}
+
 template <typename TA>
 __global__ void __launch_bounds__(128) hy_gated_norm_kernel(const float* o, int C, int group, const float* w, int wlen, const TA* gate, int ld_gate, int gate_before, int act,
                                                              const float* skip, int skip_block, const TA* xs, int ld_xs, TA* out, int ld_out, float eps) {
@@ -453,23 +549,17 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
         if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
     }
 }
-template <typename TA>
-__global__ void __launch_bounds__(128) hy_moe_router_kernel(HyRouter m, const TA* h, int ldh, const TA* wr, int ldw, const float* correction, int W, int32_t* idx, float* wgt) {
+// one warp per token: scores from the fp32 router logits, group-limited choice, weights
+__global__ void __launch_bounds__(128) hy_moe_router_kernel(HyRouter m, const float* logits, int ldz, const float* correction, int32_t* idx, float* wgt, int T) {
     extern __shared__ float sm[];
     const int E = m.experts, G = m.groups, per = E / G;
-    float* sc = sm;               // [E] sigmoid scores
-    float* ch = sm + E;           // [E] choice scores (masked: -inf)
-    float* gs = ch + E;           // [G] group scores
-    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const TA* hr = h + (long long)t * ldh;
-    for (int e = warp; e < E; e += 4) {
-        float d = 0.f;
-        for (int i = lane; i < W; i += 32) d = fmaf(ldf(hr + i), ldf(wr + (long long)e * ldw + i), d);
-        d = warp_sum(d);
-        if (lane == 0) { const float s = sigmoidf_(d); sc[e] = s; ch[e] = s + correction[e]; }
-    }
-    __syncthreads();
-    if (warp != 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = blockIdx.x * 4 + warp;
+    if (t >= T) return;
+    float* sc = sm + warp * (2 * E + G);   // [E] sigmoid scores
+    float* ch = sc + E;                    // [E] choice scores (masked: -inf)
+    float* gs = ch + E;                    // [G] group scores
+    for (int e = lane; e < E; e += 32) { const float sg = sigmoidf_(logits[(long long)t * ldz + e]); sc[e] = sg; ch[e] = sg + correction[e]; }
+    __syncwarp();
     if (G > 1 && m.keep < G) {
         for (int g = lane; g < G; g += 32) {                     // a group's score: the sum of its two largest choice scores
             float a = -INFINITY, b = -INFINITY;
@@ -533,18 +623,16 @@ __global__ void __launch_bounds__(256) hy_moe_down_kernel(const TA* act, const T
     if (lane == 0) x[(long long)t * W + n] += acc;
 }
 
-// One CTA: counts per expert, 128-row tile table, and each (token, choice)'s destination row — token order inside an expert's tiles, so
-// the plan (and with it every sum) is deterministic.
-__global__ void __launch_bounds__(1024) hy_moe_plan_kernel(const int32_t* idx, int T, int top, int E, int32_t* tile_expert, int32_t* row_src, int32_t* n_tiles_out,
-                                                           int32_t* dst_of, int max_tiles) {
-    extern __shared__ int32_t smi[];
-    int32_t* cnt = smi;           // [E]
-    int32_t* base = smi + E;      // [E] first row of the expert's tiles
-    const int n = T * top;
-    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
-    __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&cnt[idx[i]], 1);
-    __syncthreads();
+// Expert plan in three small kernels: (1) pairs per expert, (2) one CTA lays the experts' 128-row tiles out one after the other, (3) every
+// (token, choice) pair takes the next free row of its expert's tiles.  Which row of a tile a pair gets does not matter: the products treat
+// rows independently and a token's choices are added in choice order afterwards, so the result is the same for any assignment.
+__global__ void hy_moe_count_kernel(const int32_t* idx, int n, int32_t* cnt) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int e = i < n ? idx[i] : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    if (e >= 0 && (threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&cnt[e], __popc(peers));
+}
+__global__ void __launch_bounds__(1024) hy_moe_layout_kernel(int32_t* cnt, int E, int32_t* base, int32_t* tile_expert, int32_t* n_tiles_out, int max_tiles) {
     if (threadIdx.x == 0) {
         int tiles = 0;
         for (int e = 0; e < E; ++e) {
@@ -556,21 +644,19 @@ __global__ void __launch_bounds__(1024) hy_moe_plan_kernel(const int32_t* idx, i
         n_tiles_out[0] = tiles < max_tiles ? tiles : max_tiles;
     }
     __syncthreads();
-    const int tiles = n_tiles_out[0];
-    for (int i = threadIdx.x; i < tiles * 128; i += blockDim.x) row_src[i] = -1;
-    __syncthreads();
-    // rank of (token, choice) i inside its expert = number of earlier pairs routed to the same expert; one warp per expert scans in order
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    for (int e = warp; e < E; e += nw) {
-        if (cnt[e] == 0) continue;
-        int run = 0;
-        for (int i0 = 0; i0 < n; i0 += 32) {
-            const int i = i0 + lane; const bool mine = i < n && idx[i] == e;
-            const unsigned bal = __ballot_sync(0xffffffffu, mine);
-            if (mine) { const int dst = base[e] + run + __popc(bal & ((1u << lane) - 1u)); dst_of[i] = dst; row_src[dst] = i; }
-            run += __popc(bal);
-        }
-    }
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;        // reused as the fill counters of step (3)
+}
+__global__ void hy_moe_assign_kernel(const int32_t* idx, int n, const int32_t* base, int32_t* fill, int32_t* row_src, int32_t* dst_of) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int e = i < n ? idx[i] : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    if (e < 0) return;
+    const int lane = threadIdx.x & 31, leader = __ffs(peers) - 1;
+    int first = 0;
+    if (lane == leader) first = atomicAdd(&fill[e], __popc(peers));
+    first = __shfl_sync(peers, first, leader);
+    const int dst = base[e] + first + __popc(peers & ((1u << lane) - 1u));
+    dst_of[i] = dst; row_src[dst] = i;
 }
 __global__ void hy_moe_gather_kernel(const __nv_bfloat16* h, int ldh, int W, const int32_t* row_src, const int32_t* n_tiles, int top, __nv_bfloat16* out) {
     const int row = blockIdx.x;
@@ -581,11 +667,16 @@ __global__ void hy_moe_gather_kernel(const __nv_bfloat16* h, int ldh, int W, con
         *reinterpret_cast<uint4*>(out + (long long)row * W + c) = src >= 0 ? *reinterpret_cast<const uint4*>(h + (long long)(src / top) * ldh + c) : z;
 }
 __global__ void hy_moe_combine_kernel(const float* y, int ldy, const int32_t* dst_of, const float* wgt, int top, float* x, int W) {
-    const int t = blockIdx.x;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        float acc = 0.f;
-        for (int k = 0; k < top; ++k) acc = fmaf(wgt[(long long)t * top + k], y[(long long)dst_of[(long long)t * top + k] * ldy + c], acc);
-        x[(long long)t * W + c] += acc;
+    const int t = blockIdx.x;                       // W and ldy are multiples of 4 on this path
+    for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < top; ++k) {
+            const float w = wgt[(long long)t * top + k];
+            const float4 v = *reinterpret_cast<const float4*>(y + (long long)dst_of[(long long)t * top + k] * ldy + c);
+            acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+        }
+        float4* xp = reinterpret_cast<float4*>(x + (long long)t * W + c);
+        float4 xv = *xp; xv.x += acc.x; xv.y += acc.y; xv.z += acc.z; xv.w += acc.w; *xp = xv;
     }
 }
 
@@ -704,6 +795,13 @@ cudaError_t hy_mamba_prep(bool f32, const HyMamba& m, const void* conv, int ld_c
 }
 cudaError_t hy_recurrence(bool delta, const float* qq, const float* kk, const float* vv, const float* dec, const float* beta, float* out, float* state, int heads,
                           int qk_heads, int dim, int vdim, const HyRows& r, cudaStream_t s) {
+    if (dim <= 128 && dim % 4 == 0 && vdim % 4 == 0 && 3 * dim / 4 <= 96) {
+        dim3 grid(r.S, heads, (vdim + REC_CTA_COLS - 1) / REC_CTA_COLS);
+#define HY_REC(DL, DP) launch_plain(hy_recurrence_reg_kernel<DL, DP>, grid, dim3(128), (size_t)REC_STAGES * (3 * 8 * DP + 36) * 4, s, qq, kk, vv, dec, beta, out, state, heads, qk_heads, dim, vdim, r)
+        if (delta) return dim <= 32 ? HY_REC(true, 4) : dim <= 64 ? HY_REC(true, 8) : HY_REC(true, 16);
+        return dim <= 32 ? HY_REC(false, 4) : dim <= 64 ? HY_REC(false, 8) : HY_REC(false, 16);
+#undef HY_REC
+    }
     const size_t smem = (size_t)(dim * REC_COLS + 3 * dim) * 4;
     dim3 grid(r.S, heads, (vdim + REC_COLS - 1) / REC_COLS);
     static bool attr_done[2][16] = {};
@@ -720,11 +818,9 @@ cudaError_t hy_gated_norm(bool f32, const float* o, int C, int group, const floa
     return f32 ? launch_plain(hy_gated_norm_kernel<float>, grid, dim3(128), 0, s, o, C, group, w, wlen, (const float*)gate, ld_gate, gate_before, act, skip, skip_block, (const float*)xs, ld_xs, (float*)out, ld_out, eps)
                : launch_plain(hy_gated_norm_kernel<bf>, grid, dim3(128), 0, s, o, C, group, w, wlen, (const bf*)gate, ld_gate, gate_before, act, skip, skip_block, (const bf*)xs, ld_xs, (bf*)out, ld_out, eps);
 }
-cudaError_t hy_moe_router(bool f32, const HyRouter& m, const void* h, int ldh, const void* w_router, int ldw, const float* correction, int W, int32_t* idx, float* wgt,
-                          int T, cudaStream_t s) {
-    const size_t smem = (size_t)(2 * m.experts + m.groups) * 4;
-    return f32 ? launch_plain(hy_moe_router_kernel<float>, dim3(T), dim3(128), smem, s, m, (const float*)h, ldh, (const float*)w_router, ldw, correction, W, idx, wgt)
-               : launch_plain(hy_moe_router_kernel<bf>, dim3(T), dim3(128), smem, s, m, (const bf*)h, ldh, (const bf*)w_router, ldw, correction, W, idx, wgt);
+cudaError_t hy_moe_router(const HyRouter& m, const float* logits, int ldz, const float* correction, int32_t* idx, float* wgt, int T, cudaStream_t s) {
+    const size_t smem = (size_t)4 * (2 * m.experts + m.groups) * 4;
+    return launch_plain(hy_moe_router_kernel, dim3((T + 3) / 4), dim3(128), smem, s, m, logits, ldz, correction, idx, wgt, T);
 }
 cudaError_t hy_moe_gate_up(bool f32, const void* h, int ldh, const void* gu, int ldw, int W, int ff, int ffp, const int32_t* idx, int top, void* act, int T, cudaStream_t s) {
     dim3 grid(T * top, (ffp + 7) / 8);
@@ -738,7 +834,14 @@ cudaError_t hy_moe_down(bool f32, const void* act, const void* down, int W, int 
 }
 cudaError_t hy_moe_plan(const int32_t* idx, int T, int top, int experts, int32_t* tile_expert, int32_t* row_src, int32_t* n_tiles_out, int32_t* dst_of, int max_tiles,
                         cudaStream_t s) {
-    return launch_plain(hy_moe_plan_kernel, dim3(1), dim3(1024), (size_t)2 * experts * 4, s, idx, T, top, experts, tile_expert, row_src, n_tiles_out, dst_of, max_tiles);
+    // scratch after n_tiles_out[0]: [4 ..] counters [experts], then bases [experts]
+    int32_t* cnt = n_tiles_out + 4; int32_t* base = cnt + experts; const int n = T * top;
+    cudaError_t e = cudaMemsetAsync(cnt, 0, (size_t)experts * 4, s);
+    if (e != cudaSuccess) return e;
+    if ((e = cudaMemsetAsync(row_src, 0xFF, (size_t)max_tiles * 128 * 4, s)) != cudaSuccess) return e;
+    if ((e = launch_plain(hy_moe_count_kernel, dim3((n + 255) / 256), dim3(256), 0, s, idx, n, cnt)) != cudaSuccess) return e;
+    if ((e = launch_plain(hy_moe_layout_kernel, dim3(1), dim3(1024), 0, s, cnt, experts, base, tile_expert, n_tiles_out, max_tiles)) != cudaSuccess) return e;
+    return launch_plain(hy_moe_assign_kernel, dim3((n + 255) / 256), dim3(256), 0, s, idx, n, base, cnt, row_src, dst_of);
 }
 cudaError_t hy_moe_gather(const void* h, int ldh, int W, const int32_t* row_src, const int32_t* n_tiles, int top, void* out, int max_tiles, cudaStream_t s) {
     return launch_plain(hy_moe_gather_kernel, dim3(max_tiles * 128), dim3(128), 0, s, (const bf*)h, ldh, W, row_src, n_tiles, top, (bf*)out);

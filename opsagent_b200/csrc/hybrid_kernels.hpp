@@ -79,16 +79,17 @@ cudaError_t hy_gated_norm(bool f32, const float* o, int C, int group, const floa
                           const float* skip, int skip_block, const void* xs, int ld_xs, void* out, int ld_out, float eps, int T, cudaStream_t s);
 
 struct HyRouter { int experts, top, groups, keep; float scale; };
-// sigmoid router with a selection-only correction and group-limited choice: idx[t, top], wgt[t, top] (weights = chosen sigmoids / their sum * scale)
-cudaError_t hy_moe_router(bool f32, const HyRouter& m, const void* h, int ldh, const void* w_router, int ldw, const float* correction, int W,
-                          int32_t* idx, float* wgt, int T, cudaStream_t s);
+// sigmoid router over fp32 logits [T, ldz] with a selection-only correction and group-limited choice: a group's score is the sum of its two
+// largest corrected scores, only the best `keep` groups compete; idx[t, top], wgt[t, top] = chosen uncorrected sigmoids / their sum * scale
+cudaError_t hy_moe_router(const HyRouter& m, const float* logits, int ldz, const float* correction, int32_t* idx, float* wgt, int T, cudaStream_t s);
 // routed experts, one (token, choice) at a time (decode-sized batches and the fp32 mode).  gu: [E][2 ffp][ldw] with gate / up rows interleaved in
 // blocks of 16, down: [E][W][ffp]; act: [T * top, ffp]
 cudaError_t hy_moe_gate_up(bool f32, const void* h, int ldh, const void* gu, int ldw, int W, int ff, int ffp, const int32_t* idx, int top, void* act, int T, cudaStream_t s);
 cudaError_t hy_moe_down(bool f32, const void* act, const void* down, int W, int ffp, const int32_t* idx, const float* wgt, int top, float* x, int T, cudaStream_t s);
 
 // grouped (tensor-core) expert path: rows sorted by expert into 128-row tiles
-// counts -> tile table: tile_expert[n_tiles], row_src[n_tiles * 128] (token * top + choice, or -1), n_tiles_out[1]
+// counts -> tile table: tile_expert[n_tiles], row_src[max_tiles * 128] (token * top + choice, or -1), dst_of[T * top]; n_tiles_out holds the tile
+// count at [0] and 2 * experts words of scratch from [4]
 cudaError_t hy_moe_plan(const int32_t* idx, int T, int top, int experts, int32_t* tile_expert, int32_t* row_src, int32_t* n_tiles_out, int32_t* dst_of, int max_tiles, cudaStream_t s);
 cudaError_t hy_moe_gather(const void* h, int ldh, int W, const int32_t* row_src, const int32_t* n_tiles, int top, void* out, int max_tiles, cudaStream_t s);
 // x[t] += sum over choices (in order) wgt[t,c] * y[dst_of[t*top+c]]

@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <functional>
 #include <stdexcept>
 
 #include "common.cuh"
@@ -243,12 +244,13 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
     dec_ = (float*)dmalloc(MR * max_dec * 4); beta_ = (float*)dmalloc(MR * max_h * 4);
     idx_ = (int32_t*)dmalloc(MR * max_top * 4); wgt_ = (float*)dmalloc(MR * max_top * 4);
     max_tiles_ = (int)((MR * max_top + 127) / 128) + max_E;
+    rlog_ = (float*)dmalloc(MR * max_E * 4);
     bool any_moe_tc = false; for (const LayerW& w : lw_) any_moe_tc |= w.moe_tc;
     act_ = dmalloc(std::max(MR * max_act, any_moe_tc ? (size_t)max_tiles_ * 128 * max_ffp : 0) * es_);
     if (any_moe_tc) {
         moe_a_ = dmalloc((size_t)max_tiles_ * 128 * Wld_ * 2); moe_y_ = (float*)dmalloc((size_t)max_tiles_ * 128 * W * 4);
         tile_expert_ = (int32_t*)dmalloc((size_t)max_tiles_ * 4); row_src_ = (int32_t*)dmalloc((size_t)max_tiles_ * 128 * 4);
-        n_tiles_ = (int32_t*)dmalloc(16); dst_of_ = (int32_t*)dmalloc(MR * max_top * 4);
+        n_tiles_ = (int32_t*)dmalloc((size_t)(4 + 2 * max_E) * 4); dst_of_ = (int32_t*)dmalloc(MR * max_top * 4);
     }
     hs_ = dmalloc((size_t)MS_ * Wld_ * es_); logits_ = (float*)dmalloc((size_t)MS_ * V * 4); d_out_ids_ = (int32_t*)dmalloc((size_t)MS_ * 4);
     cuda_check(cudaMallocHost(&h_out_ids, (size_t)MS_ * 4), "cudaMallocHost");
@@ -323,38 +325,41 @@ void HybridModel::gemm(int mode, const void* A, int lda, const Mat& B, void* C, 
     cuda_check(launch_gemm(&tmA, &B.tm[bn == 32 ? 0 : bn == 64 ? 1 : bn == 128 ? 2 : 3], g, EPI_F32, bn, stream), "gemm (tcgen05, fp32 out)");
 }
 
-void HybridModel::moe(const LayerW& w, const HyLayer& l, const HyRows& r) {
+void HybridModel::moe(const LayerW& w, const HyLayer& l, const HyRows& r, const std::function<void(int)>& MARK) {
     const HyMoe& m = l.moe; const int W = hc_.width, T = r.T;
     HyRouter hr{m.experts, m.top, m.groups, m.keep, m.scale};
-    cuda_check(hy_moe_router(f32_, hr, h_, Wld_, w.router.p, w.router.ld, w.correction, W, idx_, wgt_, T, stream), "router");
+    // router logits: bf16 (or fp32) inputs, exact products, fp32 accumulation and output
+    gemm(HY_STORE_F32, h_, Wld_, w.router, rlog_, m.experts, T, nullptr, 1.f);
+    cuda_check(hy_moe_router(hr, rlog_, m.experts, w.correction, idx_, wgt_, T, stream), "router"); MARK(12);
     if (w.moe_tc && T >= opt.hy_moe_grouped_rows) {
         // prefill-sized batches: rows sorted by expert into 128-row tiles, two grouped tcgen05 GEMMs (SwiGLU in the first one's epilogue),
         // then each token adds its choices' rows in choice order
         const int bound = std::min(max_tiles_, (T * m.top + 127) / 128 + std::min(m.experts, T * m.top));
         cuda_check(hy_moe_plan(idx_, T, m.top, m.experts, tile_expert_, row_src_, n_tiles_, dst_of_, bound, stream), "expert plan");
-        cuda_check(hy_moe_gather(h_, Wld_, Wld_, row_src_, n_tiles_, m.top, moe_a_, bound, stream), "expert gather");
+        cuda_check(hy_moe_gather(h_, Wld_, Wld_, row_src_, n_tiles_, m.top, moe_a_, bound, stream), "expert gather"); MARK(16);
         CUtensorMap tmA, tmB;
         if (make_tmap_bf16_2d(&tmA, moe_a_, (uint64_t)bound * 128, (uint64_t)Wld_, (uint64_t)Wld_, 128, 64) != 0 ||
             make_tmap_bf16_2d(&tmB, act_, (uint64_t)bound * 128, (uint64_t)w.ffp, (uint64_t)w.ffp, 128, 64) != 0) throw std::runtime_error("tensor map for the expert activations failed");
         GemmParams g{}; g.M = bound * 128; g.N = 2 * w.ffp; g.K = Wld_; g.out = act_; g.ldo = w.ffp;
         g.m_tile_group = tile_expert_; g.n_m_tiles = n_tiles_; g.group_rows = 2 * w.ffp;
         const int bn1 = 2 * w.ffp >= 256 ? 256 : 128;
-        cuda_check(launch_gemm(&tmA, &w.tm_gu[bn1 == 256], g, EPI_SWIGLU, bn1, stream), "experts gate/up (grouped tcgen05)");
+        cuda_check(launch_gemm(&tmA, &w.tm_gu[bn1 == 256], g, EPI_SWIGLU, bn1, stream), "experts gate/up (grouped tcgen05)"); MARK(17);
         GemmParams d{}; d.M = bound * 128; d.N = W; d.K = w.ffp; d.f32_out = moe_y_; d.ldf = W; d.alpha = 1.f;
         d.m_tile_group = tile_expert_; d.n_m_tiles = n_tiles_; d.group_rows = W;
         const int bn2 = W >= 256 ? 256 : 128;
-        cuda_check(launch_gemm(&tmB, &w.tm_down[bn2 == 256], d, EPI_F32, bn2, stream), "experts down (grouped tcgen05)");
-        cuda_check(hy_moe_combine(moe_y_, W, dst_of_, wgt_, m.top, x_, W, T, stream), "expert combine");
+        cuda_check(launch_gemm(&tmB, &w.tm_down[bn2 == 256], d, EPI_F32, bn2, stream), "experts down (grouped tcgen05)"); MARK(18);
+        cuda_check(hy_moe_combine(moe_y_, W, dst_of_, wgt_, m.top, x_, W, T, stream), "expert combine"); MARK(19);
         return;
     }
     cuda_check(hy_moe_gate_up(f32_, h_, Wld_, w.gu, Wld_, W, m.ff, w.ffp, idx_, m.top, act_, T, stream), "experts gate/up");
-    cuda_check(hy_moe_down(f32_, act_, w.down, W, w.ffp, idx_, wgt_, m.top, x_, T, stream), "experts down");
+    cuda_check(hy_moe_down(f32_, act_, w.down, W, w.ffp, idx_, wgt_, m.top, x_, T, stream), "experts down"); MARK(13);
 }
 
 const char* HybridModel::kt_name(int id) const {
-    static const char* n[16] = {"h2d+embed", "layer_norm", "in_proj_gemm", "latent_absorb+up_gemm", "latent_cache_write", "latent_attention", "conv", "recurrence_prep",
-                                "recurrence", "gated_norm", "low_rank_gemm", "out_proj_gemm", "router", "experts", "loop_in", "head+argmax"};
-    return n[id & 15];
+    static const char* n[32] = {"h2d+embed", "layer_norm", "in_proj_gemm", "latent_absorb+up_gemm", "latent_cache_write", "latent_attention", "conv", "recurrence_prep",
+                                "recurrence", "gated_norm", "low_rank_gemm", "out_proj_gemm", "router", "experts_per_token", "loop_in", "head+argmax",
+                                "expert_plan+gather", "expert_gate_up_gemm", "expert_down_gemm", "expert_combine", "", "", "", "", "", "", "", "", "", "", "", ""};
+    return n[id & 31];
 }
 
 void HybridModel::forward(const StepInput& in, float* logits_out) {
@@ -407,12 +412,12 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
 
     size_t ek = 0;
     if (profile_all) {
-        const size_t need = hc_.runs.size() * 16 + 16;
+        const size_t need = hc_.runs.size() * 24 + 16;
         if (ev_all.size() < need) { size_t o = ev_all.size(); ev_all.resize(need); for (size_t i = o; i < need; ++i) cudaEventCreate(&ev_all[i]); }
         ev_ids.assign(ev_all.size(), 0);
         cudaEventRecord(ev_all[ek++], stream);
     }
-    auto MARK = [&](int id) { if (profile_all && ek < ev_all.size()) { ev_ids[ek] = id; cudaEventRecord(ev_all[ek++], stream); } };
+    const std::function<void(int)> MARK = [&](int id) { if (profile_all && ek < ev_all.size()) { ev_ids[ek] = id; cudaEventRecord(ev_all[ek++], stream); } };
     cuda_check(hy_embed(f32_, d_meta_ + o_tok, embed_, x_, x0_, T, W, V, stream), "embed"); MARK(0);
     auto at = [&](void* base, size_t elems) -> void* { return reinterpret_cast<char*>(base) + elems * es_; };
     for (const HyRun& run : hc_.runs) {
@@ -458,7 +463,7 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
                                      hc_.eps, T, stream), "gated norm"); MARK(9);
         }
         gemm(HY_ACC_F32, mix_, ld_mix_, w.o, x_, W, T, nullptr, 1.f); MARK(11);
-        if (l.moe.present) { moe(w, l, r); MARK(13); }
+        if (l.moe.present) moe(w, l, r, MARK);
         if (capture_layers) {
             cuda_check(cudaStreamSynchronize(stream), "capture sync");
             const size_t n0 = capture_layers->size(); capture_layers->resize(n0 + (size_t)T * W);
@@ -479,7 +484,7 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
     }
     if (profile_all) {
         cuda_check(cudaStreamSynchronize(stream), "profile sync");
-        for (size_t i = 1; i < ek; ++i) { float ms = 0; cudaEventElapsedTime(&ms, ev_all[i - 1], ev_all[i]); kt_ms[ev_ids[i] & 15] += ms; kt_n[ev_ids[i] & 15]++; }
+        for (size_t i = 1; i < ek; ++i) { float ms = 0; cudaEventElapsedTime(&ms, ev_all[i - 1], ev_all[i]); kt_ms[ev_ids[i] & 31] += ms; kt_n[ev_ids[i] & 31]++; }
     }
 }
 

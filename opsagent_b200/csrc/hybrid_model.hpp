@@ -3,6 +3,7 @@
 // tokens alike), attention layers keep their compressed keys in the engine's 64-token pages, recurrent layers keep an fp32 state and their
 // convolution tails in the sequence's state slot.
 #pragma once
+#include <functional>
 #include <string>
 #include <vector>
 
@@ -47,7 +48,7 @@ private:
     HostMat tensor(const std::string& name, int N, int K);                // checkpoint tensor (or seeded values) as fp32 [N, K]; K == 0: any width
     std::vector<float> vec(const std::string& name, int n, float init_mean, float init_spread);
     void gemm(int mode, const void* A, int lda, const Mat& B, void* C, int ldc, int M, const float* bias, float alpha);
-    void moe(const LayerW& w, const HyLayer& l, const HyRows& r);
+    void moe(const LayerW& w, const HyLayer& l, const HyRows& r, const std::function<void(int)>& mark);
 
     HybridConfig hc_; bool f32_ = false; size_t es_ = 2;
     struct SafeTensorsHolder; SafeTensorsHolder* st_ = nullptr;
@@ -59,7 +60,7 @@ private:
     int MR_ = 0, MS_ = 0, Wld_ = 0;
     // activations
     float *x_ = nullptr, *x0_ = nullptr, *q_abs_ = nullptr, *qq_ = nullptr, *kk_ = nullptr, *vv_ = nullptr, *dec_ = nullptr, *beta_ = nullptr, *rec_ = nullptr, *wgt_ = nullptr,
-          *logits_ = nullptr, *moe_y_ = nullptr;
+          *logits_ = nullptr, *moe_y_ = nullptr, *rlog_ = nullptr;
     void *cat_ = nullptr, *h_ = nullptr, *proj_ = nullptr, *p2_ = nullptr, *conv_ = nullptr, *lat_ = nullptr, *mix_ = nullptr, *act_ = nullptr, *hs_ = nullptr, *moe_a_ = nullptr;
     int ld_proj_ = 0, ld_p2_ = 0, ld_conv_ = 0, ld_mix_ = 0;
     int32_t *idx_ = nullptr, *d_out_ids_ = nullptr, *tile_expert_ = nullptr, *row_src_ = nullptr, *n_tiles_ = nullptr, *dst_of_ = nullptr; int max_tiles_ = 0;

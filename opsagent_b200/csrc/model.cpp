@@ -311,7 +311,7 @@ DeviceModel::~DeviceModel() {
 const char* ModelBase::kt_name(int id) const {
     static const char* n[16] = {"h2d+embed", "rmsnorm", "qkv_gemm", "rope_kv", "attention", "attn_merge", "o_gemm", "resid_rmsnorm", "gate_up_gemm",
                                 "swiglu", "down_gemm", "gather+norm", "lm_head", "argmax+d2h", "", ""};
-    return n[id & 15];
+    return (id & 31) < 16 ? n[id & 15] : "";
 }
 void ModelBase::sync() { cuda_check(cudaStreamSynchronize(stream), "stream sync"); }
 

@@ -67,8 +67,8 @@ public:
     // instrumentation
     bool profile_attn = false; double attn_ms_accum = 0; std::vector<cudaEvent_t> ev;
     // in-situ per-kernel timing (events after every launch, warm caches, real launch gaps): OA_PROFILE_ALL=1
-    bool profile_all = false; std::vector<cudaEvent_t> ev_all; std::vector<int> ev_ids; double kt_ms[16] = {0}; long kt_n[16] = {0};
-    virtual const char* kt_name(int id) const;      // name of in-situ timing class id (0..15)
+    bool profile_all = false; std::vector<cudaEvent_t> ev_all; std::vector<int> ev_ids; double kt_ms[32] = {0}; long kt_n[32] = {0};
+    virtual const char* kt_name(int id) const;      // name of in-situ timing class id (0..31; "" = unused)
     uint64_t h2d_bytes = 0, d2h_bytes = 0;
 };
 std::unique_ptr<ModelBase> make_model(const ModelConfig& cfg, const EngineOptions& opt);
