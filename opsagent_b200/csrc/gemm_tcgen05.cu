@@ -298,12 +298,13 @@ cudaError_t launch_gemm(const CUtensorMap* tmA, const CUtensorMap* tmB, const Ge
     if (epilogue == EPI_SWIGLU && (p.N % 32) != 0) return cudaErrorInvalidValue;
     // large-M (prefill) shapes with the widest tile go to the persistent kernel (epilogue overlapped with the next tile)
     if (epilogue == EPI_F32 && ((p.ldf % 4) != 0 || !p.f32_out)) return cudaErrorInvalidValue;
-    if (block_n == 256 && epilogue != EPI_LOGITS && epilogue != EPI_F32 && !p.m_tile_group && !persistent_disabled() &&
+    if (block_n == 256 && epilogue != EPI_LOGITS && !persistent_disabled() &&
         (long long)((p.N + 255) / 256) * ((p.M + BLOCK_M - 1) / BLOCK_M) >= persistent_min_tiles()) {
         switch (epilogue) {
             case EPI_STORE: return launch_persistent<EPI_STORE>(tmA, tmB, p, stream);
             case EPI_RESID: return launch_persistent<EPI_RESID>(tmA, tmB, p, stream);
             case EPI_SWIGLU: return launch_persistent<EPI_SWIGLU>(tmA, tmB, p, stream);
+            case EPI_F32: return launch_persistent<EPI_F32>(tmA, tmB, p, stream);
         }
     }
     switch (block_n) {
@@ -353,7 +354,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_persistent_kernel(const 
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_tiles = (p.N + BN - 1) / BN, m_tiles = (p.M + BLOCK_M - 1) / BLOCK_M;
+    const int n_tiles = (p.N + BN - 1) / BN;
+    int m_tiles = (p.M + BLOCK_M - 1) / BLOCK_M;
+    if (p.m_tile_group) {                 // grouped product: the number of live row tiles comes from the device (possibly from the preceding kernel)
+        griddep_wait();
+        const int live = *p.n_m_tiles;
+        if (live < m_tiles) m_tiles = live;
+    }
     const int total_tiles = n_tiles * m_tiles;
     const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
 
@@ -376,12 +383,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_persistent_kernel(const 
             int s = 0; uint32_t ph = 0;
             for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
                 int m_blk, n_blk; raster_tile(t, m_tiles, n_tiles, m_blk, n_blk);
+                const int b_row0 = n_blk * BN + (p.m_tile_group ? p.m_tile_group[m_blk] * p.group_rows : 0);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     mbar_wait(&empty_bar[s], ph ^ 1);
                     uint8_t* a_dst = smem + s * Cfg::STAGE_BYTES;
                     mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
                     tma_load_2d(a_dst, &tmA, &full_bar[s], kb * BLOCK_K, m_blk * BLOCK_M, kEvictNormal);
-                    tma_load_2d(a_dst + Cfg::A_BYTES, &tmB, &full_bar[s], kb * BLOCK_K, n_blk * BN, kEvictNormal);
+                    tma_load_2d(a_dst + Cfg::A_BYTES, &tmB, &full_bar[s], kb * BLOCK_K, b_row0, kEvictNormal);
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
             }
@@ -459,7 +467,22 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_persistent_kernel(const 
                         const float* sp = stage + r * Cfg::EPI_ROW_FLOATS + c8;
                         const float4 a0 = *reinterpret_cast<const float4*>(sp), a1 = *reinterpret_cast<const float4*>(sp + 4);
                         float f[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                        if (row < p.M && col < p.N) {
+                        if (EPI == EPI_F32) {
+                            if (row < p.M && col < p.N) {
+                                const float al = p.alpha == 0.f ? 1.f : p.alpha;
+                                float* op = p.f32_out + (size_t)row * p.ldf + col;
+                                float4 o0 = make_float4(f[0] * al, f[1] * al, f[2] * al, f[3] * al), o1 = make_float4(f[4] * al, f[5] * al, f[6] * al, f[7] * al);
+                                if (p.bias_f32) {
+                                    const float4 b0 = *reinterpret_cast<const float4*>(p.bias_f32 + col), b1 = *reinterpret_cast<const float4*>(p.bias_f32 + col + 4);
+                                    o0.x += b0.x; o0.y += b0.y; o0.z += b0.z; o0.w += b0.w; o1.x += b1.x; o1.y += b1.y; o1.z += b1.z; o1.w += b1.w;
+                                }
+                                if (p.f32_accumulate) {
+                                    const float4 r0 = *reinterpret_cast<const float4*>(op), r1 = *reinterpret_cast<const float4*>(op + 4);
+                                    o0.x += r0.x; o0.y += r0.y; o0.z += r0.z; o0.w += r0.w; o1.x += r1.x; o1.y += r1.y; o1.z += r1.z; o1.w += r1.w;
+                                }
+                                *reinterpret_cast<float4*>(op) = o0; *reinterpret_cast<float4*>(op + 4) = o1;
+                            }
+                        } else if (row < p.M && col < p.N) {
                             if (EPI == EPI_STORE) {
                                 if (p.bias) {
                                     const uint4 bb = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col);

@@ -658,6 +658,31 @@ __global__ void hy_moe_assign_kernel(const int32_t* idx, int n, const int32_t* b
     const int dst = base[e] + first + __popc(peers & ((1u << lane) - 1u));
     dst_of[i] = dst; row_src[dst] = i;
 }
+// the same plan in one CTA for decode-sized steps (n = T * top pairs): counters live in shared memory
+__global__ void __launch_bounds__(1024) hy_moe_plan_small_kernel(const int32_t* idx, int n, int E, int32_t* tile_expert, int32_t* row_src, int32_t* n_tiles_out,
+                                                                 int32_t* dst_of, int max_tiles) {
+    extern __shared__ int32_t plan_sm[];
+    int32_t* cnt = plan_sm; int32_t* base = plan_sm + E; __shared__ int tiles_sh;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&cnt[idx[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tiles = 0;
+        for (int e = 0; e < E; ++e) {
+            base[e] = tiles * 128;
+            const int nt = (cnt[e] + 127) / 128;
+            for (int k = 0; k < nt && tiles + k < max_tiles; ++k) tile_expert[tiles + k] = e;
+            tiles += nt;
+        }
+        tiles_sh = tiles < max_tiles ? tiles : max_tiles; n_tiles_out[0] = tiles_sh;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < tiles_sh * 128; i += blockDim.x) row_src[i] = -1;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { const int e = idx[i], dst = base[e] + atomicAdd(&cnt[e], 1); dst_of[i] = dst; row_src[dst] = i; }
+}
 __global__ void hy_moe_gather_kernel(const __nv_bfloat16* h, int ldh, int W, const int32_t* row_src, const int32_t* n_tiles, int top, __nv_bfloat16* out) {
     const int row = blockIdx.x;
     if (row >= n_tiles[0] * 128) return;
@@ -764,11 +789,11 @@ cudaError_t hy_mla_attention_mma(const HyLatentAttn& a, const float* q_abs, cons
     dim3 grid(n_tiles, a.kv_rank / (nvb * 8));
     static bool done[3][16] = {};
     cudaError_t e;
-    if (nvb == 32) { if ((e = ensure_dynamic_smem(hy_mla_attention_mma_kernel<32>, (int)smem, done[0])) != cudaSuccess) return e;
+    if (nvb == 32) { if ((e = ensure_dynamic_smem(hy_mla_attention_mma_kernel<32>, 200 * 1024, done[0])) != cudaSuccess) return e;
         return launch_plain(hy_mla_attention_mma_kernel<32>, grid, dim3(128), smem, s, a, q_abs, (const bf*)cache, (bf*)lat_out, r, tile_seq, tile_q0); }
-    if (nvb == 16) { if ((e = ensure_dynamic_smem(hy_mla_attention_mma_kernel<16>, (int)smem, done[1])) != cudaSuccess) return e;
+    if (nvb == 16) { if ((e = ensure_dynamic_smem(hy_mla_attention_mma_kernel<16>, 200 * 1024, done[1])) != cudaSuccess) return e;
         return launch_plain(hy_mla_attention_mma_kernel<16>, grid, dim3(128), smem, s, a, q_abs, (const bf*)cache, (bf*)lat_out, r, tile_seq, tile_q0); }
-    if ((e = ensure_dynamic_smem(hy_mla_attention_mma_kernel<8>, (int)smem, done[2])) != cudaSuccess) return e;
+    if ((e = ensure_dynamic_smem(hy_mla_attention_mma_kernel<8>, 200 * 1024, done[2])) != cudaSuccess) return e;
     return launch_plain(hy_mla_attention_mma_kernel<8>, grid, dim3(128), smem, s, a, q_abs, (const bf*)cache, (bf*)lat_out, r, tile_seq, tile_q0);
 }
 cudaError_t hy_conv_silu(bool f32, const void* in, int ld_in, int C, const float* w, const float* bias, int taps, void* out, int ld_out, const void* tails, const HyRows& r,
@@ -805,8 +830,9 @@ cudaError_t hy_recurrence(bool delta, const float* qq, const float* kk, const fl
     const size_t smem = (size_t)(dim * REC_COLS + 3 * dim) * 4;
     dim3 grid(r.S, heads, (vdim + REC_COLS - 1) / REC_COLS);
     static bool attr_done[2][16] = {};
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
     if (smem > 48 * 1024) {
-        cudaError_t e = delta ? ensure_dynamic_smem(hy_recurrence_kernel<true>, (int)smem, attr_done[0]) : ensure_dynamic_smem(hy_recurrence_kernel<false>, (int)smem, attr_done[1]);
+        cudaError_t e = delta ? ensure_dynamic_smem(hy_recurrence_kernel<true>, 200 * 1024, attr_done[0]) : ensure_dynamic_smem(hy_recurrence_kernel<false>, 200 * 1024, attr_done[1]);      // the limit is set once per kernel and device: raise it to the most any size may ask for
         if (e != cudaSuccess) return e;
     }
     return delta ? launch_plain(hy_recurrence_kernel<true>, grid, dim3(REC_COLS), smem, s, qq, kk, vv, dec, beta, out, state, heads, qk_heads, dim, vdim, r)
@@ -836,6 +862,7 @@ cudaError_t hy_moe_plan(const int32_t* idx, int T, int top, int experts, int32_t
                         cudaStream_t s) {
     // scratch after n_tiles_out[0]: [4 ..] counters [experts], then bases [experts]
     int32_t* cnt = n_tiles_out + 4; int32_t* base = cnt + experts; const int n = T * top;
+    if (n <= 4096) return launch_plain(hy_moe_plan_small_kernel, dim3(1), dim3(1024), (size_t)2 * experts * 4, s, idx, n, experts, tile_expert, row_src, n_tiles_out, dst_of, max_tiles);
     cudaError_t e = cudaMemsetAsync(cnt, 0, (size_t)experts * 4, s);
     if (e != cudaSuccess) return e;
     if ((e = cudaMemsetAsync(row_src, 0xFF, (size_t)max_tiles * 128 * 4, s)) != cudaSuccess) return e;
