@@ -197,8 +197,8 @@ __global__ void __launch_bounds__(128) hy_mla_attention_kernel(HyLatentAttn a, c
 // O += P V are mma.sync m16n8k16 products on the same shared-memory tile (the cached row is key AND value); softmax is online, in fp32
 // registers, with the mask applied per query position.  A CTA accumulates NVB * 8 of the latent's channels (blockIdx.y picks which).
 // ---------------------------------------------------------------------------------------------------------------------------------
-constexpr int MLA_MQ = 64, MLA_KT = 32;
-template <int NVB>
+constexpr int MLA_MQ = 64;
+template <int NVB, int MLA_KT>      // MLA_KT = cache rows per tile: 32, or 16 where that lets two CTAs share an SM
 __global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn a, const float* __restrict__ q_abs, const __nv_bfloat16* __restrict__ cache,
                                                                    __nv_bfloat16* __restrict__ lat_out, HyRows r, const int32_t* __restrict__ tile_seq,
                                                                    const int32_t* __restrict__ tile_q0) {
@@ -244,9 +244,10 @@ __global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn 
         __syncthreads();
         if (active) {
             const __nv_bfloat16* Kb = Ks + (kt & 1) * MLA_KT * EP;
-            float s[4][4];
+            constexpr int NB = MLA_KT / 8;
+            float s[NB][4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+            for (int i = 0; i < NB; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
             const uint32_t qa = smem_u32(Qs + (16 * warp + (lane & 15)) * EP + (lane >> 4) * 8);
             const uint32_t ka = smem_u32(Kb + ((lane >> 4) * 8 + (lane & 7)) * EP + ((lane >> 3) & 1) * 8);
             for (int ks = 0; ks < E / 16; ++ks) {
@@ -254,13 +255,15 @@ __global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn 
                 ldmatrix_x4(qa + ks * 32, a0, a1, a2, a3);
                 ldmatrix_x4(ka + ks * 32, b0, b1, b2, b3);
                 mma_bf16_16816(s[0], a0, a1, a2, a3, b0, b1); mma_bf16_16816(s[1], a0, a1, a2, a3, b2, b3);
-                ldmatrix_x4(ka + 16 * EP * 2 + ks * 32, b0, b1, b2, b3);
-                mma_bf16_16816(s[2], a0, a1, a2, a3, b0, b1); mma_bf16_16816(s[3], a0, a1, a2, a3, b2, b3);
+                if (NB == 4) {
+                    ldmatrix_x4(ka + 16 * EP * 2 + ks * 32, b0, b1, b2, b3);
+                    mma_bf16_16816(s[NB - 2], a0, a1, a2, a3, b0, b1); mma_bf16_16816(s[NB - 1], a0, a1, a2, a3, b2, b3);
+                }
             }
             const int p_lo = qpos[16 * warp + (lane >> 2)], p_hi = qpos[16 * warp + (lane >> 2) + 8];
             float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
-            for (int nb = 0; nb < 4; ++nb)
+            for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const int key = kt * MLA_KT + nb * 8 + (lane & 3) * 2 + (c & 1);
@@ -274,7 +277,7 @@ __global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn 
             m_lo = n_lo; m_hi = n_hi;
             float sum_lo = 0.f, sum_hi = 0.f;
 #pragma unroll
-            for (int nb = 0; nb < 4; ++nb) {
+            for (int nb = 0; nb < NB; ++nb) {
                 s[nb][0] = exp2f(s[nb][0] - n_lo); s[nb][1] = exp2f(s[nb][1] - n_lo); s[nb][2] = exp2f(s[nb][2] - n_hi); s[nb][3] = exp2f(s[nb][3] - n_hi);
                 sum_lo += s[nb][0] + s[nb][1]; sum_hi += s[nb][2] + s[nb][3];
             }
@@ -283,7 +286,7 @@ __global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn 
             for (int i = 0; i < NVB; ++i) { o[i][0] *= c_lo; o[i][1] *= c_lo; o[i][2] *= c_hi; o[i][3] *= c_hi; }
             const uint32_t va = smem_u32(Kb + (((lane >> 3) & 1) * 8 + (lane & 7)) * EP + vbase + (lane >> 4) * 8);
 #pragma unroll
-            for (int kk = 0; kk < 2; ++kk) {
+            for (int kk = 0; kk < NB / 2; ++kk) {
                 const uint32_t a0 = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]), a1 = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
                 const uint32_t a2 = pack_bf16x2(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = pack_bf16x2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
@@ -417,53 +420,48 @@ __global__ void __launch_bounds__(REC_COLS) hy_recurrence_kernel(const float* qq
     if (ok) for (int d = 0; d < D; ++d) st[(long long)d * VD + col] = S[d * REC_COLS + j];
 }
 
-// Register-resident variant for dim <= 8 * DP (dim and vdim multiples of 4): a thread owns two state columns (value channels), each split
-// over 8 lanes that hold DP of its rows in registers; the dot products of a step meet through three shuffles.  The per-token operands
-// (q, k, decay slices, 32 values, the scalar) arrive through an 8-deep cp.async ring in shared memory — every copying thread keeps its own
-// source pointer and advances it by a constant per token — so a step never waits on global memory and spends few instructions outside the
-// multiply-adds.  32 columns per 128-thread CTA: even one decoding sequence spreads over heads x vdim / 32 CTAs.  The order of every sum is
-// fixed (lane-local rows ascending in two interleaved chains, then the shuffle tree), whatever else the step holds.
-constexpr int REC_STAGES = 8, REC_CTA_COLS = 32;
-template <bool DELTA, int DP>
+// Register-resident variant for dim <= DM (dim and vdim multiples of 4): a state column (value channel) lives in the registers of LANES
+// adjacent lanes (LANES = 1: one thread holds all DM rows and a step needs no cross-lane traffic; LANES = 4: four lanes hold a quarter each
+// and the two dot products of a step meet through two shuffles — four times the threads for steps with few sequences).  The per-token operands (q, k, decay rows, 128 values, the scalar)
+// arrive through an 8-deep cp.async ring in shared memory — every thread keeps its own source pointer and advances it by a constant per
+// token — and are read from there as 16-byte broadcasts.  The dependent chains of a step are split over four accumulators.  128 / LANES
+// columns per CTA.  The order of every sum is fixed for a given LANES, and LANES is chosen from the sizes alone, never from the step.
+constexpr int REC_STAGES = 8, REC_CTA_COLS = 128;
+template <bool DELTA, int DM, int LANES>
 __global__ void __launch_bounds__(128) hy_recurrence_reg_kernel(const float* __restrict__ qq, const float* __restrict__ kk, const float* __restrict__ vv,
                                                                 const float* __restrict__ dec, const float* __restrict__ beta, float* __restrict__ out,
                                                                 float* __restrict__ state, int H, int QH, int D, int VD, HyRows r) {
     extern __shared__ __align__(16) float rec_ring[];
-    constexpr int DPAD = 8 * DP;                    // rows padded to the lanes' slices: pad rows hold q = k = 0, decay 1, so they stay zero
-    constexpr int stride = 3 * DPAD + 36;           // floats per stage: q[DPAD] k[DPAD] g[DPAD] v[32] scalar (padded to 16 bytes)
-    const int tid = threadIdx.x, part = tid & 7, cl = tid >> 3, col = blockIdx.z * REC_CTA_COLS + 2 * cl;
+    constexpr int stride = 3 * DM + REC_CTA_COLS + 4;     // floats per stage: q[DM] k[DM] g[DM] v[128] scalar (padded to 16 bytes); pad rows: q = k = 0, decay 1
+    constexpr int DR = DM / LANES, COLS = REC_CTA_COLS / LANES;       // rows per thread, columns per CTA
+    const int tid = threadIdx.x, part = tid % LANES, cl = tid / LANES, col = blockIdx.z * COLS + cl, r0 = part * DR;
     const int seq = blockIdx.x, h = blockIdx.y;
-    const bool ok0 = col < VD, ok1 = col + 1 < VD;
-    const int row0 = r.seq_row0[seq], len = r.seq_row0[seq + 1] - row0, pos0 = r.seq_pos0[seq], qh = h / (H / QH), d0 = part * DP;
+    const bool ok = col < VD;
+    const int row0 = r.seq_row0[seq], len = r.seq_row0[seq + 1] - row0, pos0 = r.seq_pos0[seq], qh = h / (H / QH);
     float* st = state + ((long long)r.seq_state[seq] * H + h) * D * VD;
-    float S0[DP], S1[DP];
+    float S[DR];
 #pragma unroll
-    for (int i = 0; i < DP; ++i) {
-        const bool in = pos0 > 0 && d0 + i < D;
-        S0[i] = (ok0 && in) ? st[(long long)(d0 + i) * VD + col] : 0.f; S1[i] = (ok1 && in) ? st[(long long)(d0 + i) * VD + col + 1] : 0.f;
-    }
-    for (int i = tid; i < REC_STAGES * stride; i += 128) { const int w = i % stride; rec_ring[i] = (w >= 2 * DPAD && w < 3 * DPAD) ? 1.f : 0.f; }
+    for (int i = 0; i < DR; ++i) S[i] = (ok && pos0 > 0 && r0 + i < D) ? st[(long long)(r0 + i) * VD + col] : 0.f;
+    for (int i = tid; i < REC_STAGES * stride; i += 128) { const int w = i % stride; rec_ring[i] = (w >= 2 * DM && w < 3 * DM) ? 1.f : 0.f; }
     __syncthreads();
-    // this thread's copy role: one 16-byte piece (or the 4-byte scalar) per token, source advancing by `step` floats per token
+    // this thread's copy roles: one 16-byte piece per token (threads 0..95: q / k / decay rows, 96..127: the values), thread 0 also the scalar
     const int dq = D / 4, n_vec = (DELTA ? 3 : 2) * dq;
-    const float* src = nullptr; int dst = 0, bytes = 0; long long step = 0;
+    const float* src = nullptr; int dst = 0; long long step = 0;
     if (tid < n_vec) {
         const int which = tid / dq, c = tid - which * dq;
         src = (which == 0 ? qq + ((long long)row0 * QH + qh) * D : which == 1 ? kk + ((long long)row0 * QH + qh) * D : dec + ((long long)row0 * H + h) * D) + c * 4;
-        step = which == 2 ? (long long)H * D : (long long)QH * D; dst = which * DPAD + c * 4; bytes = 16;
-    } else if (tid >= 96 && tid < 104) {
+        step = which == 2 ? (long long)H * D : (long long)QH * D; dst = which * DM + c * 4;
+    } else if (tid >= 96) {
         const int c = tid - 96;
-        if (blockIdx.z * REC_CTA_COLS + c * 4 < VD) { src = vv + ((long long)row0 * H + h) * VD + blockIdx.z * REC_CTA_COLS + c * 4; step = (long long)H * VD; dst = 3 * DPAD + c * 4; bytes = 16; }
-    } else if (tid == 104) {
-        src = (DELTA ? beta : dec) + (long long)row0 * H + h; step = H; dst = 3 * DPAD + 32; bytes = 4;
+        if (c * 4 < COLS && blockIdx.z * COLS + c * 4 < VD) { src = vv + ((long long)row0 * H + h) * VD + blockIdx.z * COLS + c * 4; step = (long long)H * VD; dst = 3 * DM + c * 4; }
     }
+    const float* src_sc = tid == 0 ? (DELTA ? beta : dec) + (long long)row0 * H + h : nullptr;
     int issued = 0;
     auto issue = [&]() {                             // next token of the sequence's rows -> ring slot issued % REC_STAGES
-        if (issued < len && bytes) {
-            float* d = rec_ring + (issued % REC_STAGES) * stride + dst;
-            if (bytes == 16) cp_async16(d, src);
-            else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(d)), "l"(src) : "memory");
-            src += step;
+        if (issued < len) {
+            float* slot = rec_ring + (issued % REC_STAGES) * stride;
+            if (src) { cp_async16(slot + dst, src); src += step; }
+            if (src_sc) { asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(slot + 3 * DM + REC_CTA_COLS)), "l"(src_sc) : "memory"); src_sc += H; }
         }
         ++issued;
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -475,41 +473,42 @@ __global__ void __launch_bounds__(128) hy_recurrence_reg_kernel(const float* __r
         __syncthreads();                             // token i has landed for everybody; slot (i - 1) % STAGES is free again
         issue();
         const float* slot = rec_ring + (i % REC_STAGES) * stride;
-        const float2 v = *reinterpret_cast<const float2*>(slot + 3 * DPAD + 2 * cl); const float sc = slot[3 * DPAD + 32];
-        float q[DP], k[DP];
-#pragma unroll
-        for (int j = 0; j < DP; j += 4) {
-            const float4 q4 = *reinterpret_cast<const float4*>(slot + d0 + j), k4 = *reinterpret_cast<const float4*>(slot + DPAD + d0 + j);
-            q[j] = q4.x; q[j + 1] = q4.y; q[j + 2] = q4.z; q[j + 3] = q4.w; k[j] = k4.x; k[j + 1] = k4.y; k[j + 2] = k4.z; k[j + 3] = k4.w;
-        }
-        float o0 = 0.f, o1 = 0.f;
+        const float v = slot[3 * DM + cl], sc = slot[3 * DM + REC_CTA_COLS];
+        const float* sq = slot + r0; const float* sk = slot + DM + r0; const float* sg = slot + 2 * DM + r0;
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
         if (DELTA) {
-            float dot0 = 0.f, dot1 = 0.f;
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
-            for (int j = 0; j < DP; j += 4) {
-                const float4 g4 = *reinterpret_cast<const float4*>(slot + 2 * DPAD + d0 + j);
-                S0[j] *= g4.x; S0[j + 1] *= g4.y; S0[j + 2] *= g4.z; S0[j + 3] *= g4.w; S1[j] *= g4.x; S1[j + 1] *= g4.y; S1[j + 2] *= g4.z; S1[j + 3] *= g4.w;
-#pragma unroll
-                for (int u = 0; u < 4; ++u) { dot0 = fmaf(S0[j + u], k[j + u], dot0); dot1 = fmaf(S1[j + u], k[j + u], dot1); }
+            for (int j = 0; j < DR; j += 4) {
+                const float4 g4 = *reinterpret_cast<const float4*>(sg + j), k4 = *reinterpret_cast<const float4*>(sk + j);
+                S[j] *= g4.x; S[j + 1] *= g4.y; S[j + 2] *= g4.z; S[j + 3] *= g4.w;
+                d0 = fmaf(S[j], k4.x, d0); d1 = fmaf(S[j + 1], k4.y, d1); d2 = fmaf(S[j + 2], k4.z, d2); d3 = fmaf(S[j + 3], k4.w, d3);
             }
-            dot0 += __shfl_xor_sync(0xffffffffu, dot0, 1); dot1 += __shfl_xor_sync(0xffffffffu, dot1, 1);
-            dot0 += __shfl_xor_sync(0xffffffffu, dot0, 2); dot1 += __shfl_xor_sync(0xffffffffu, dot1, 2);
-            dot0 += __shfl_xor_sync(0xffffffffu, dot0, 4); dot1 += __shfl_xor_sync(0xffffffffu, dot1, 4);
-            const float u0 = sc * (v.x - dot0), u1 = sc * (v.y - dot1);
+            float dot = (d0 + d1) + (d2 + d3);
+            if (LANES == 4) { dot += __shfl_xor_sync(0xffffffffu, dot, 1); dot += __shfl_xor_sync(0xffffffffu, dot, 2); }
+            const float u = sc * (v - dot);
 #pragma unroll
-            for (int j = 0; j < DP; ++j) { S0[j] = fmaf(k[j], u0, S0[j]); S1[j] = fmaf(k[j], u1, S1[j]); o0 = fmaf(S0[j], q[j], o0); o1 = fmaf(S1[j], q[j], o1); }
+            for (int j = 0; j < DR; j += 4) {
+                const float4 q4 = *reinterpret_cast<const float4*>(sq + j), k4 = *reinterpret_cast<const float4*>(sk + j);
+                S[j] = fmaf(k4.x, u, S[j]); S[j + 1] = fmaf(k4.y, u, S[j + 1]); S[j + 2] = fmaf(k4.z, u, S[j + 2]); S[j + 3] = fmaf(k4.w, u, S[j + 3]);
+                o0 = fmaf(S[j], q4.x, o0); o1 = fmaf(S[j + 1], q4.y, o1); o2 = fmaf(S[j + 2], q4.z, o2); o3 = fmaf(S[j + 3], q4.w, o3);
+            }
         } else {
 #pragma unroll
-            for (int j = 0; j < DP; ++j) { S0[j] = fmaf(k[j], v.x, S0[j] * sc); S1[j] = fmaf(k[j], v.y, S1[j] * sc); o0 = fmaf(S0[j], q[j], o0); o1 = fmaf(S1[j], q[j], o1); }
+            for (int j = 0; j < DR; j += 4) {
+                const float4 q4 = *reinterpret_cast<const float4*>(sq + j), k4 = *reinterpret_cast<const float4*>(sk + j);
+                S[j] = fmaf(k4.x, v, S[j] * sc); S[j + 1] = fmaf(k4.y, v, S[j + 1] * sc); S[j + 2] = fmaf(k4.z, v, S[j + 2] * sc); S[j + 3] = fmaf(k4.w, v, S[j + 3] * sc);
+                o0 = fmaf(S[j], q4.x, o0); o1 = fmaf(S[j + 1], q4.y, o1); o2 = fmaf(S[j + 2], q4.z, o2); o3 = fmaf(S[j + 3], q4.w, o3);
+            }
         }
-        o0 += __shfl_xor_sync(0xffffffffu, o0, 1); o1 += __shfl_xor_sync(0xffffffffu, o1, 1);
-        o0 += __shfl_xor_sync(0xffffffffu, o0, 2); o1 += __shfl_xor_sync(0xffffffffu, o1, 2);
-        o0 += __shfl_xor_sync(0xffffffffu, o0, 4); o1 += __shfl_xor_sync(0xffffffffu, o1, 4);
-        if (part == 0) { if (ok1) *reinterpret_cast<float2*>(op) = make_float2(o0, o1); else if (ok0) *op = o0; }
+        float o = (o0 + o1) + (o2 + o3);
+        if (LANES == 4) { o += __shfl_xor_sync(0xffffffffu, o, 1); o += __shfl_xor_sync(0xffffffffu, o, 2); }
+        if (ok && part == 0) *op = o;
         op += (long long)H * VD;
     }
+    if (ok)
 #pragma unroll
-    for (int i = 0; i < DP; ++i) if (d0 + i < D) { if (ok0) st[(long long)(d0 + i) * VD + col] = S0[i]; if (ok1) st[(long long)(d0 + i) * VD + col + 1] = S1[i]; }
+        for (int i = 0; i < DR; ++i) if (r0 + i < D) st[(long long)(r0 + i) * VD + col] = S[i];
 }
 
 template <typename TA>
@@ -773,28 +772,34 @@ cudaError_t hy_mla_attention(bool f32, const HyLatentAttn& a, const float* q_abs
     return f32 ? launch_plain(hy_mla_attention_kernel<float>, dim3(r.T, a.heads), dim3(128), smem, s, a, q_abs, (const float*)cache, (float*)lat_out, r)
                : launch_plain(hy_mla_attention_kernel<bf>, dim3(r.T, a.heads), dim3(128), smem, s, a, q_abs, (const bf*)cache, (bf*)lat_out, r);
 }
+static size_t mla_mma_smem(int E, int kt) { return (size_t)(MLA_MQ + 2 * kt) * (E + 8) * 2 + MLA_MQ * 4; }
 static int mla_mma_nvb(const HyLatentAttn& a) {
     const int E = a.kv_rank + a.rot_dim;
     if (E % 16 != 0 || a.kv_rank % 64 != 0) return 0;
     const int nvb = a.kv_rank % 256 == 0 ? 32 : (a.kv_rank % 128 == 0 ? 16 : 8);
-    const size_t smem = (size_t)(MLA_MQ + 2 * MLA_KT) * (E + 8) * 2 + MLA_MQ * 4;
-    return smem <= 200 * 1024 ? nvb : 0;
+    return mla_mma_smem(E, 16) <= 200 * 1024 ? nvb : 0;
 }
 bool hy_mla_mma_supported(const HyLatentAttn& a) { return mla_mma_nvb(a) != 0; }
+template <int NVB, int KT>
+static cudaError_t mla_mma_launch(const HyLatentAttn& a, const float* q_abs, const void* cache, void* lat_out, const HyRows& r, const int32_t* tile_seq,
+                                  const int32_t* tile_q0, int n_tiles, cudaStream_t s) {
+    static bool done[16] = {};
+    cudaError_t e = ensure_dynamic_smem(hy_mla_attention_mma_kernel<NVB, KT>, 200 * 1024, done);      // set once per device: the most any size asks for
+    if (e != cudaSuccess) return e;
+    dim3 grid(n_tiles, a.kv_rank / (NVB * 8));
+    return launch_plain(hy_mla_attention_mma_kernel<NVB, KT>, grid, dim3(128), mla_mma_smem(a.kv_rank + a.rot_dim, KT), s, a, q_abs, (const bf*)cache, (bf*)lat_out, r,
+                        tile_seq, tile_q0);
+}
 cudaError_t hy_mla_attention_mma(const HyLatentAttn& a, const float* q_abs, const void* cache, void* lat_out, const HyRows& r, const int32_t* tile_seq,
                                  const int32_t* tile_q0, int n_tiles, cudaStream_t s) {
     const int nvb = mla_mma_nvb(a), E = a.kv_rank + a.rot_dim;
     if (!nvb) return cudaErrorInvalidValue;
-    const size_t smem = (size_t)(MLA_MQ + 2 * MLA_KT) * (E + 8) * 2 + MLA_MQ * 4;
-    dim3 grid(n_tiles, a.kv_rank / (nvb * 8));
-    static bool done[3][16] = {};
-    cudaError_t e;
-    if (nvb == 32) { if ((e = ensure_dynamic_smem(hy_mla_attention_mma_kernel<32>, 200 * 1024, done[0])) != cudaSuccess) return e;
-        return launch_plain(hy_mla_attention_mma_kernel<32>, grid, dim3(128), smem, s, a, q_abs, (const bf*)cache, (bf*)lat_out, r, tile_seq, tile_q0); }
-    if (nvb == 16) { if ((e = ensure_dynamic_smem(hy_mla_attention_mma_kernel<16>, 200 * 1024, done[1])) != cudaSuccess) return e;
-        return launch_plain(hy_mla_attention_mma_kernel<16>, grid, dim3(128), smem, s, a, q_abs, (const bf*)cache, (bf*)lat_out, r, tile_seq, tile_q0); }
-    if ((e = ensure_dynamic_smem(hy_mla_attention_mma_kernel<8>, 200 * 1024, done[2])) != cudaSuccess) return e;
-    return launch_plain(hy_mla_attention_mma_kernel<8>, grid, dim3(128), smem, s, a, q_abs, (const bf*)cache, (bf*)lat_out, r, tile_seq, tile_q0);
+    // 32-row tiles when two CTAs (8 warps) still fit an SM's shared memory or nothing smaller would make them fit; else 16-row tiles
+    // (a step with few tiles — decoding — is a latency chain per CTA: the larger tile halves its length)
+    const bool kt32 = mla_mma_smem(E, 32) <= 113 * 1024 || mla_mma_smem(E, 16) > 113 * 1024 || n_tiles * (a.kv_rank / (nvb * 8)) < 296;
+#define HY_MLA(NVB) (kt32 ? mla_mma_launch<NVB, 32>(a, q_abs, cache, lat_out, r, tile_seq, tile_q0, n_tiles, s) : mla_mma_launch<NVB, 16>(a, q_abs, cache, lat_out, r, tile_seq, tile_q0, n_tiles, s))
+    return nvb == 32 ? HY_MLA(32) : nvb == 16 ? HY_MLA(16) : HY_MLA(8);
+#undef HY_MLA
 }
 cudaError_t hy_conv_silu(bool f32, const void* in, int ld_in, int C, const float* w, const float* bias, int taps, void* out, int ld_out, const void* tails, const HyRows& r,
                          cudaStream_t s) {
@@ -820,11 +825,18 @@ cudaError_t hy_mamba_prep(bool f32, const HyMamba& m, const void* conv, int ld_c
 }
 cudaError_t hy_recurrence(bool delta, const float* qq, const float* kk, const float* vv, const float* dec, const float* beta, float* out, float* state, int heads,
                           int qk_heads, int dim, int vdim, const HyRows& r, cudaStream_t s) {
-    if (dim <= 128 && dim % 4 == 0 && vdim % 4 == 0 && 3 * dim / 4 <= 96) {
-        dim3 grid(r.S, heads, (vdim + REC_CTA_COLS - 1) / REC_CTA_COLS);
-#define HY_REC(DL, DP) launch_plain(hy_recurrence_reg_kernel<DL, DP>, grid, dim3(128), (size_t)REC_STAGES * (3 * 8 * DP + 36) * 4, s, qq, kk, vv, dec, beta, out, state, heads, qk_heads, dim, vdim, r)
-        if (delta) return dim <= 32 ? HY_REC(true, 4) : dim <= 64 ? HY_REC(true, 8) : HY_REC(true, 16);
-        return dim <= 32 ? HY_REC(false, 4) : dim <= 64 ? HY_REC(false, 8) : HY_REC(false, 16);
+    if (dim <= 128 && dim % 4 == 0 && vdim % 4 == 0) {
+        // measured (batch 16 x 1024 tokens, dim 128): four lanes per column 23.1 ms against 7.3 ms with one, although it has four times
+        // the warps — the broadcast reads of a warp become four-way, and the shuffles join the chain.  One lane per column everywhere.
+        const bool wide = false;
+        dim3 grid(r.S, heads, (vdim * (wide ? 4 : 1) + REC_CTA_COLS - 1) / REC_CTA_COLS);
+        const int dm = dim <= 32 ? 32 : dim <= 64 ? 64 : 128;
+        const size_t ring = (size_t)REC_STAGES * (3 * dm + REC_CTA_COLS + 4) * 4;
+#define HY_REC(DL, DM, LN) launch_plain(hy_recurrence_reg_kernel<DL, DM, LN>, grid, dim3(128), ring, s, qq, kk, vv, dec, beta, out, state, heads, qk_heads, dim, vdim, r)
+#define HY_REC_DM(DL, LN) (dm == 32 ? HY_REC(DL, 32, LN) : dm == 64 ? HY_REC(DL, 64, LN) : HY_REC(DL, 128, LN))
+        if (delta) return wide ? HY_REC_DM(true, 4) : HY_REC_DM(true, 1);
+        return wide ? HY_REC_DM(false, 4) : HY_REC_DM(false, 1);
+#undef HY_REC_DM
 #undef HY_REC
     }
     const size_t smem = (size_t)(dim * REC_COLS + 3 * dim) * 4;
