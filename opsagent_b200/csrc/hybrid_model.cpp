@@ -156,6 +156,18 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
             w.uk_t = upload_act(ukt);
             w.uv = upload_act(tensor(mx + "uv", l.heads * l.vdim, l.kv_rank).v);
             w.o = upload_mat(tensor(mx + "o", W, l.heads * l.vdim));
+            if (!f32_ && opt.hy_tensor_core && l.dim % 8 == 0 && l.rot_dim % 8 == 0 && l.kv_rank % 8 == 0 && l.vdim % 8 == 0) {
+                const int bns[4] = {32, 64, 128, 256}; bool all = true;
+                for (int h = 0; h < l.heads && all; ++h) {
+                    Mat a; a.p = reinterpret_cast<char*>(w.uk_t) + (size_t)h * l.kv_rank * l.dim * 2; a.N = l.kv_rank; a.K = a.ld = l.dim; a.tc = true;
+                    Mat b; b.p = reinterpret_cast<char*>(w.uv) + (size_t)h * l.vdim * l.kv_rank * 2; b.N = l.vdim; b.K = b.ld = l.kv_rank; b.tc = true;
+                    for (int i = 0; i < 4; ++i)
+                        all = all && make_tmap_bf16_2d(&a.tm[i], a.p, (uint64_t)a.N, (uint64_t)a.ld, (uint64_t)a.ld, (uint32_t)bns[i], 64) == 0 &&
+                              make_tmap_bf16_2d(&b.tm[i], b.p, (uint64_t)b.N, (uint64_t)b.ld, (uint64_t)b.ld, (uint32_t)bns[i], 64) == 0;
+                    w.uk_heads.push_back(a); w.uv_heads.push_back(b);
+                }
+                if (!all) { w.uk_heads.clear(); w.uv_heads.clear(); }
+            }
             for (size_t i = 0; i < ropes_.size(); ++i) if (ropes_[i].base == l.rot_base && ropes_[i].dims == l.rot_dims) w.rope = (int)i;
             if (w.rope < 0) {
                 RopeTable rt; rt.base = l.rot_base; rt.dims = l.rot_dims; const int half = l.rot_dims / 2;
@@ -432,16 +444,21 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
             const HyLatentAttn a{l.heads, l.dim, l.rot_dim, l.vdim, l.kv_rank, l.rot_dims, l.scale};
             const int E = l.kv_rank + l.rot_dim;
             // absorbed queries: q_abs[t, h, :rank] = W_uk[h]^T q_unrotated[t, h]
-            cuda_check(hy_gemm(f32_, HY_STORE_F32, at(proj_, w.off_a), ld_proj_, w.uk_t, l.dim, q_abs_, l.heads * E, T, l.kv_rank, l.dim, nullptr, 1.f, l.heads,
-                               l.dim + l.rot_dim, (long long)l.kv_rank * l.dim, E, stream), "query absorption"); MARK(3);
+            const bool head_tc = !w.uk_heads.empty() && T >= 256;      // prefill-sized steps: one tcgen05 GEMM per head; smaller ones: one batched launch
+            if (head_tc) for (int hd = 0; hd < l.heads; ++hd) gemm(HY_STORE_F32, at(proj_, w.off_a + (size_t)hd * (l.dim + l.rot_dim)), ld_proj_, w.uk_heads[hd], q_abs_ + (size_t)hd * E, l.heads * E, T, nullptr, 1.f);
+            else cuda_check(hy_gemm(f32_, HY_STORE_F32, at(proj_, w.off_a), ld_proj_, w.uk_t, l.dim, q_abs_, l.heads * E, T, l.kv_rank, l.dim, nullptr, 1.f, l.heads,
+                                    l.dim + l.rot_dim, (long long)l.kv_rank * l.dim, E, stream), "query absorption");
+            MARK(3);
             cuda_check(hy_mla_prep(f32_, a, at(proj_, w.off_a), ld_proj_, at(proj_, w.off_b), ld_proj_, w.dkv_norm, hc_.eps, ropes_[w.rope].cos, ropes_[w.rope].sin,
                                    caches_[run.cache_idx], q_abs_, r, stream), "latent cache write"); MARK(4);
             const TileList* tl = nullptr; for (const TileList& t : tile_lists) if (t.heads == l.heads && hy_mla_mma_supported(a)) tl = &t;
             if (tl) cuda_check(hy_mla_attention_mma(a, q_abs_, caches_[run.cache_idx], lat_, r, d_meta_ + tl->o_seq, d_meta_ + tl->o_q0, tl->n, stream), "latent attention (mma)");
             else cuda_check(hy_mla_attention(f32_, a, q_abs_, caches_[run.cache_idx], lat_, r, stream), "latent attention");
             MARK(5);
-            cuda_check(hy_gemm(f32_, HY_STORE, lat_, l.heads * l.kv_rank, w.uv, l.kv_rank, mix_, ld_mix_, T, l.vdim, l.kv_rank, nullptr, 1.f, l.heads, l.kv_rank,
-                               (long long)l.vdim * l.kv_rank, l.vdim, stream), "value up-projection"); MARK(3);
+            if (head_tc) for (int hd = 0; hd < l.heads; ++hd) gemm(HY_STORE, at(lat_, (size_t)hd * l.kv_rank), l.heads * l.kv_rank, w.uv_heads[hd], at(mix_, (size_t)hd * l.vdim), ld_mix_, T, nullptr, 1.f);
+            else cuda_check(hy_gemm(f32_, HY_STORE, lat_, l.heads * l.kv_rank, w.uv, l.kv_rank, mix_, ld_mix_, T, l.vdim, l.kv_rank, nullptr, 1.f, l.heads, l.kv_rank,
+                                    (long long)l.vdim * l.kv_rank, l.vdim, stream), "value up-projection");
+            MARK(3);
         } else if (l.type == HY_CHANNEL_DELTA) {
             const HyDelta d{l.heads, l.kv_heads, l.dim, l.vdim};
             cuda_check(hy_conv_silu(f32_, at(proj_, w.off_a), ld_proj_, w.conv_ch, w.conv_w, nullptr, l.conv, conv_, ld_conv_, tails_[run.state_idx], r, stream), "conv");

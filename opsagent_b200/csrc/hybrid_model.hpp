@@ -34,6 +34,7 @@ private:
         int off_a = 0, off_b = 0, off_c = 0, off_d = 0;   // column offsets of the fused input projection's segments (see hybrid_model.cpp)
         int a_rank = 0, g_rank = 0;
         void *uk_t = nullptr, *uv = nullptr; float* dkv_norm = nullptr; int rope = -1;      // latent attention
+        std::vector<Mat> uk_heads, uv_heads;          // per-head views of uk_t / uv with tensor maps (prefill-sized steps run them on the tensor cores)
         float *A_log = nullptr, *dt_bias = nullptr, *norm_w = nullptr, *conv_w = nullptr, *conv_b = nullptr, *D = nullptr;
         int conv_ch = 0;
         float* correction = nullptr; void *gu = nullptr, *down = nullptr; int ffp = 0;       // experts: gu [E][2 ffp][ldw], down [E][W][ffp]
