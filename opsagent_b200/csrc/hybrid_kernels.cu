@@ -148,7 +148,7 @@ __global__ void __launch_bounds__(128) hy_mla_prep_kernel(HyLatentAttn a, const 
     }
 }
 
-constexpr int MLA_ACC = 16;     // latent channels per lane: kv_rank <= 32 * MLA_ACC
+constexpr int MLA_ACC = 32;     // latent channels per lane: kv_rank <= 32 * MLA_ACC
 template <typename TA>
 __global__ void __launch_bounds__(128) hy_mla_attention_kernel(HyLatentAttn a, const float* q_abs, const TA* cache, TA* lat_out, HyRows r) {
     extern __shared__ float sm[];

@@ -245,7 +245,7 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
     delete st_; st_ = nullptr;
 
     // ---- activations ----
-    MR_ = std::max(opt.max_step_tokens, opt.max_batch); MS_ = std::max(opt.max_batch, std::min(MR_, 4096));
+    MR_ = std::max(opt.max_step_tokens, opt.max_batch); MS_ = MR_;      // every row of a step may be asked for (the caller then brings the logits buffer)
     const size_t MR = (size_t)MR_;
     x_ = (float*)dmalloc(MR * W * 4); x0_ = (float*)dmalloc(MR * W * 4);
     cat_ = dmalloc(MR * 2 * Wld_ * es_); h_ = dmalloc(MR * Wld_ * es_);
@@ -264,7 +264,7 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
         tile_expert_ = (int32_t*)dmalloc((size_t)max_tiles_ * 4); row_src_ = (int32_t*)dmalloc((size_t)max_tiles_ * 128 * 4);
         n_tiles_ = (int32_t*)dmalloc((size_t)(4 + 2 * max_E) * 4); dst_of_ = (int32_t*)dmalloc(MR * max_top * 4);
     }
-    hs_ = dmalloc((size_t)MS_ * Wld_ * es_); logits_ = (float*)dmalloc((size_t)MS_ * V * 4); d_out_ids_ = (int32_t*)dmalloc((size_t)MS_ * 4);
+    hs_ = dmalloc((size_t)MS_ * Wld_ * es_); logits_ = (float*)dmalloc((size_t)opt.max_batch * V * 4);      // own logits: sampling steps only (one row per sequence) d_out_ids_ = (int32_t*)dmalloc((size_t)MS_ * 4);
     cuda_check(cudaMallocHost(&h_out_ids, (size_t)MS_ * 4), "cudaMallocHost");
     mask_words = (V + 31) / 32; mask_slots = 0; max_mask_updates = 0;       // grammar-constrained sampling is not wired to this family's head
 
@@ -493,6 +493,7 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
     }
     if (NS > 0) {
         cuda_check(hy_layernorm(f32_, x_, d_meta_ + o_samp, final_norm_, hs_, Wld_, NS, W, hc_.eps, stream), "final norm");
+        if (!logits_out && NS > opt.max_batch) throw std::runtime_error("forward: more sampled rows than sequences need a caller's logits buffer");
         float* lg = logits_out ? logits_out : logits_;
         gemm(HY_STORE_F32, hs_, Wld_, head_, lg, V, NS, nullptr, hc_.logit_scale);
         cuda_check(hy_argmax_rows(lg, NS, V, d_out_ids_, stream), "argmax");

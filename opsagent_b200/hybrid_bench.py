@@ -11,7 +11,7 @@ import tempfile
 
 def sizes(name: str) -> dict:
     if name == "small":
-        att = {"heads": 8, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256, "scale": 96 ** -0.5, "rot": {"base": 10000.0, "dims": 32}}
+        att = {"heads": 16, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256, "scale": 96 ** -0.5, "rot": {"base": 10000.0, "dims": 32}}
         dl = {"heads": 8, "kv_heads": 4, "dim": 64, "vdim": 128, "conv": 4}
         mb = {"heads": 16, "vdim": 64, "state": 64, "groups": 2, "norm_groups": 1, "conv": 4}
         moe = {"kind": "moe", "expert": {"ff": 512}, "router": {"experts": 16, "top": 4, "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
