@@ -3,6 +3,8 @@
 #include <cuda_bf16.h>
 #include <math.h>
 
+#include <utility>
+
 #include "hybrid_kernels.hpp"
 #include "kernels.hpp"
 #include "common.cuh"
@@ -39,11 +41,13 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
 }
 
+// Every kernel of this file opens with HY_PDL(): it lets the next kernel of the stream become resident early (programmatic dependent
+// launch) and then waits until every predecessor grid has completed and its memory is visible — nothing is read or written before that, so
+// the kernels stay strictly ordered; what overlaps is only the launch latency and the ramp of the next grid.
+#define HY_PDL() do { griddep_launch(); griddep_wait(); } while (0)
 template <typename... KArgs, typename... Args>
 cudaError_t launch_plain(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
-    count_launch();
-    kern<<<grid, block, smem, st>>>(KArgs(args)...);
-    return cudaGetLastError();
+    return launch_k(kern, grid, block, smem, st, std::forward<Args>(args)...);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------------
@@ -53,6 +57,7 @@ cudaError_t launch_plain(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t s
 template <typename TA, int MODE>
 __global__ void __launch_bounds__(256) hy_gemm_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ B, int ldb, void* Cv, int ldc, int M, int N, int K,
                                                       const float* __restrict__ bias, float alpha, long long sA, long long sB, long long sC) {
+    HY_PDL();
     __shared__ float As[16][64 + 4], Bs[16][64 + 4];
     A += (long long)blockIdx.z * sA; B += (long long)blockIdx.z * sB;
     const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64, tid = threadIdx.x;
@@ -96,16 +101,19 @@ __global__ void __launch_bounds__(256) hy_gemm_kernel(const TA* __restrict__ A, 
 
 template <typename TA>
 __global__ void hy_embed_kernel(const int32_t* ids, const TA* table, float* x, float* x0, int T, int W, int vocab) {
+    HY_PDL();
     const int t = blockIdx.x; int id = ids[t]; id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
     for (int c = threadIdx.x; c < W; c += blockDim.x) { const float v = ldf(table + (long long)id * W + c); x[(long long)t * W + c] = v; x0[(long long)t * W + c] = v; }
 }
 template <typename TA>
 __global__ void hy_concat_kernel(const float* x, const float* x0, TA* cat, int T, int W) {
+    HY_PDL();
     const int t = blockIdx.x;
     for (int c = threadIdx.x; c < W; c += blockDim.x) { stf(cat + (long long)t * 2 * W + c, x[(long long)t * W + c]); stf(cat + (long long)t * 2 * W + W + c, x0[(long long)t * W + c]); }
 }
 template <typename TA>
 __global__ void __launch_bounds__(256) hy_layernorm_kernel(const float* x, const int32_t* rows, const float* w, TA* out, int ldo, int W, float eps) {
+    HY_PDL();
     __shared__ float red[32];
     const int t = blockIdx.x; const float* xr = x + (long long)(rows ? rows[t] : t) * W;
     float s = 0.f;
@@ -123,6 +131,7 @@ __global__ void __launch_bounds__(256) hy_layernorm_kernel(const float* x, const
 template <typename TA>
 __global__ void __launch_bounds__(128) hy_mla_prep_kernel(HyLatentAttn a, const TA* q, int ldq, const TA* ckv, int ldc, const float* norm_w, float eps,
                                                            const float* rope_cos, const float* rope_sin, TA* cache, float* q_abs, HyRows r) {
+    HY_PDL();
     __shared__ float red[32];
     const int t = blockIdx.x, R = a.kv_rank, rot = a.rot_dim, half = a.rot_dims / 2, E = R + rot;
     const TA* c = ckv + (long long)t * ldc;
@@ -151,6 +160,7 @@ __global__ void __launch_bounds__(128) hy_mla_prep_kernel(HyLatentAttn a, const 
 constexpr int MLA_ACC = 32;     // latent channels per lane: kv_rank <= 32 * MLA_ACC
 template <typename TA>
 __global__ void __launch_bounds__(128) hy_mla_attention_kernel(HyLatentAttn a, const float* q_abs, const TA* cache, TA* lat_out, HyRows r) {
+    HY_PDL();
     extern __shared__ float sm[];
     const int t = blockIdx.x, h = blockIdx.y, R = a.kv_rank, E = R + a.rot_dim;
     float* qs = sm;                      // [E]
@@ -202,6 +212,7 @@ template <int NVB, int MLA_KT>      // MLA_KT = cache rows per tile: 32, or 16 w
 __global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn a, const float* __restrict__ q_abs, const __nv_bfloat16* __restrict__ cache,
                                                                    __nv_bfloat16* __restrict__ lat_out, HyRows r, const int32_t* __restrict__ tile_seq,
                                                                    const int32_t* __restrict__ tile_q0) {
+    HY_PDL();
     extern __shared__ __align__(16) uint8_t mla_smem[];
     const int R = a.kv_rank, E = R + a.rot_dim, EP = E + 8, H = a.heads;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(mla_smem);      // [MLA_MQ][EP]
@@ -326,6 +337,7 @@ __device__ __forceinline__ float conv_input(const TA* in, int ld_in, int C, cons
 }
 template <typename TA>
 __global__ void hy_conv_silu_kernel(const TA* in, int ld_in, int C, const float* w, const float* bias, int taps, TA* out, int ld_out, const TA* tails, HyRows r) {
+    HY_PDL();
     const int c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
     if (c >= C) return;
     const int seq = r.row_seq[t], row0 = r.seq_row0[seq], i = t - row0, pos0 = r.seq_pos0[seq];
@@ -336,6 +348,7 @@ __global__ void hy_conv_silu_kernel(const TA* in, int ld_in, int C, const float*
 }
 template <typename TA>
 __global__ void hy_conv_tails_kernel(const TA* in, int ld_in, int C, int taps, TA* tails, HyRows r) {
+    HY_PDL();
     const int c = blockIdx.x * blockDim.x + threadIdx.x, seq = blockIdx.y;
     if (c >= C) return;
     const int row0 = r.seq_row0[seq], len = r.seq_row0[seq + 1] - row0, pos0 = r.seq_pos0[seq];
@@ -351,6 +364,7 @@ __global__ void hy_conv_tails_kernel(const TA* in, int ld_in, int C, int taps, T
 template <typename TA>
 __global__ void __launch_bounds__(128) hy_delta_prep_kernel(HyDelta d, const TA* conv, int ld_conv, const TA* b, int ld_b, const TA* a, int ld_a, const float* A_log,
                                                              const float* dt_bias, float* qq, float* kk, float* vv, float* dec, float* beta) {
+    HY_PDL();
     const int t = blockIdx.x, KH = d.kv_heads, H = d.heads, D = d.dim, VD = d.vdim;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const TA* cr = conv + (long long)t * ld_conv;
@@ -371,6 +385,7 @@ __global__ void __launch_bounds__(128) hy_delta_prep_kernel(HyDelta d, const TA*
 template <typename TA>
 __global__ void __launch_bounds__(128) hy_mamba_prep_kernel(HyMamba m, const TA* conv, int ld_conv, const TA* dt, int ld_dt, const float* A_log, const float* dt_bias,
                                                              float* qq, float* kk, float* vv, float* dec) {
+    HY_PDL();
     const int t = blockIdx.x, H = m.heads, VD = m.vdim, N = m.state, G = m.groups, inner = H * VD;
     const TA* cr = conv + (long long)t * ld_conv;
     for (int i = threadIdx.x; i < G * N; i += blockDim.x) { kk[(long long)t * G * N + i] = ldf(cr + inner + i); qq[(long long)t * G * N + i] = ldf(cr + inner + G * N + i); }
@@ -388,6 +403,7 @@ constexpr int REC_COLS = 64;      // state columns (value channels) per CTA; a c
 template <bool DELTA>
 __global__ void __launch_bounds__(REC_COLS) hy_recurrence_kernel(const float* qq, const float* kk, const float* vv, const float* dec, const float* beta, float* out,
                                                                  float* state, int H, int QH, int D, int VD, HyRows r) {
+    HY_PDL();
     extern __shared__ float sm[];
     float* S = sm;                         // [D][REC_COLS]
     float* qs = S + D * REC_COLS; float* ks = qs + D; float* ds = ks + D;
@@ -431,6 +447,7 @@ template <bool DELTA, int DM, int LANES>
 __global__ void __launch_bounds__(128) hy_recurrence_reg_kernel(const float* __restrict__ qq, const float* __restrict__ kk, const float* __restrict__ vv,
                                                                 const float* __restrict__ dec, const float* __restrict__ beta, float* __restrict__ out,
                                                                 float* __restrict__ state, int H, int QH, int D, int VD, HyRows r) {
+    HY_PDL();
     extern __shared__ __align__(16) float rec_ring[];
     constexpr int stride = 3 * DM + REC_CTA_COLS + 4;     // floats per stage: q[DM] k[DM] g[DM] v[128] scalar (padded to 16 bytes); pad rows: q = k = 0, decay 1
     constexpr int DR = DM / LANES, COLS = REC_CTA_COLS / LANES;       // rows per thread, columns per CTA
@@ -514,6 +531,7 @@ __global__ void __launch_bounds__(128) hy_recurrence_reg_kernel(const float* __r
 template <typename TA>
 __global__ void __launch_bounds__(128) hy_gated_norm_kernel(const float* o, int C, int group, const float* w, int wlen, const TA* gate, int ld_gate, int gate_before, int act,
                                                              const float* skip, int skip_block, const TA* xs, int ld_xs, TA* out, int ld_out, float eps) {
+    HY_PDL();
     __shared__ float red[32];
     const int t = blockIdx.x, c0 = blockIdx.y * group;
     float ss = 0.f;
@@ -550,6 +568,7 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 }
 // one warp per token: scores from the fp32 router logits, group-limited choice, weights
 __global__ void __launch_bounds__(128) hy_moe_router_kernel(HyRouter m, const float* logits, int ldz, const float* correction, int32_t* idx, float* wgt, int T) {
+    HY_PDL();
     extern __shared__ float sm[];
     const int E = m.experts, G = m.groups, per = E / G;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = blockIdx.x * 4 + warp;
@@ -593,6 +612,7 @@ __global__ void __launch_bounds__(128) hy_moe_router_kernel(HyRouter m, const fl
 
 template <typename TA>
 __global__ void __launch_bounds__(256) hy_moe_gate_up_kernel(const TA* h, int ldh, const TA* gu, int ldw, int W, int ff, int ffp, const int32_t* idx, int top, TA* act) {
+    HY_PDL();
     const int row = blockIdx.x, t = row / top, e = idx[row], warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int f = blockIdx.y * 8 + warp;
     if (f >= ffp) return;
@@ -608,6 +628,7 @@ __global__ void __launch_bounds__(256) hy_moe_gate_up_kernel(const TA* h, int ld
 }
 template <typename TA>
 __global__ void __launch_bounds__(256) hy_moe_down_kernel(const TA* act, const TA* down, int W, int ffp, const int32_t* idx, const float* wgt, int top, float* x) {
+    HY_PDL();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = blockIdx.y * 8 + warp;
     if (n >= W) return;
     float acc = 0.f;
@@ -626,12 +647,14 @@ __global__ void __launch_bounds__(256) hy_moe_down_kernel(const TA* act, const T
 // (token, choice) pair takes the next free row of its expert's tiles.  Which row of a tile a pair gets does not matter: the products treat
 // rows independently and a token's choices are added in choice order afterwards, so the result is the same for any assignment.
 __global__ void hy_moe_count_kernel(const int32_t* idx, int n, int32_t* cnt) {
+    HY_PDL();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const int e = i < n ? idx[i] : -1;
     const unsigned peers = __match_any_sync(0xffffffffu, e);
     if (e >= 0 && (threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&cnt[e], __popc(peers));
 }
 __global__ void __launch_bounds__(1024) hy_moe_layout_kernel(int32_t* cnt, int E, int32_t* base, int32_t* tile_expert, int32_t* n_tiles_out, int max_tiles) {
+    HY_PDL();
     if (threadIdx.x == 0) {
         int tiles = 0;
         for (int e = 0; e < E; ++e) {
@@ -646,6 +669,7 @@ __global__ void __launch_bounds__(1024) hy_moe_layout_kernel(int32_t* cnt, int E
     for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;        // reused as the fill counters of step (3)
 }
 __global__ void hy_moe_assign_kernel(const int32_t* idx, int n, const int32_t* base, int32_t* fill, int32_t* row_src, int32_t* dst_of) {
+    HY_PDL();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const int e = i < n ? idx[i] : -1;
     const unsigned peers = __match_any_sync(0xffffffffu, e);
@@ -660,6 +684,7 @@ __global__ void hy_moe_assign_kernel(const int32_t* idx, int n, const int32_t* b
 // the same plan in one CTA for decode-sized steps (n = T * top pairs): counters live in shared memory
 __global__ void __launch_bounds__(1024) hy_moe_plan_small_kernel(const int32_t* idx, int n, int E, int32_t* tile_expert, int32_t* row_src, int32_t* n_tiles_out,
                                                                  int32_t* dst_of, int max_tiles) {
+    HY_PDL();
     extern __shared__ int32_t plan_sm[];
     int32_t* cnt = plan_sm; int32_t* base = plan_sm + E; __shared__ int tiles_sh;
     for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
@@ -683,6 +708,7 @@ __global__ void __launch_bounds__(1024) hy_moe_plan_small_kernel(const int32_t* 
     for (int i = threadIdx.x; i < n; i += blockDim.x) { const int e = idx[i], dst = base[e] + atomicAdd(&cnt[e], 1); dst_of[i] = dst; row_src[dst] = i; }
 }
 __global__ void hy_moe_gather_kernel(const __nv_bfloat16* h, int ldh, int W, const int32_t* row_src, const int32_t* n_tiles, int top, __nv_bfloat16* out) {
+    HY_PDL();
     const int row = blockIdx.x;
     if (row >= n_tiles[0] * 128) return;
     const int src = row_src[row];
@@ -691,6 +717,7 @@ __global__ void hy_moe_gather_kernel(const __nv_bfloat16* h, int ldh, int W, con
         *reinterpret_cast<uint4*>(out + (long long)row * W + c) = src >= 0 ? *reinterpret_cast<const uint4*>(h + (long long)(src / top) * ldh + c) : z;
 }
 __global__ void hy_moe_combine_kernel(const float* y, int ldy, const int32_t* dst_of, const float* wgt, int top, float* x, int W) {
+    HY_PDL();
     const int t = blockIdx.x;                       // W and ldy are multiples of 4 on this path
     for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -705,10 +732,12 @@ __global__ void hy_moe_combine_kernel(const float* y, int ldy, const int32_t* ds
 }
 
 __global__ void hy_gather_rows_f32_kernel(const float* x, const int32_t* rows, float* out, int W) {
+    HY_PDL();
     const int i = blockIdx.x;
     for (int c = threadIdx.x; c < W; c += blockDim.x) out[(long long)i * W + c] = x[(long long)rows[i] * W + c];
 }
 __global__ void __launch_bounds__(256) hy_argmax_rows_kernel(const float* logits, int V, int32_t* out_ids) {
+    HY_PDL();
     __shared__ float bv[8]; __shared__ int bi[8];
     const float* lr = logits + (long long)blockIdx.x * V;
     float v = -INFINITY; int i = 0x7fffffff;
@@ -722,6 +751,7 @@ __global__ void __launch_bounds__(256) hy_argmax_rows_kernel(const float* logits
     }
 }
 __global__ void hy_add_rowvec_kernel(float* x, const float* v, int W) {
+    HY_PDL();
     for (int c = threadIdx.x; c < W; c += blockDim.x) x[(long long)blockIdx.x * W + c] += v[c];
 }
 

@@ -264,7 +264,8 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
         tile_expert_ = (int32_t*)dmalloc((size_t)max_tiles_ * 4); row_src_ = (int32_t*)dmalloc((size_t)max_tiles_ * 128 * 4);
         n_tiles_ = (int32_t*)dmalloc((size_t)(4 + 2 * max_E) * 4); dst_of_ = (int32_t*)dmalloc(MR * max_top * 4);
     }
-    hs_ = dmalloc((size_t)MS_ * Wld_ * es_); logits_ = (float*)dmalloc((size_t)opt.max_batch * V * 4);      // own logits: sampling steps only (one row per sequence) d_out_ids_ = (int32_t*)dmalloc((size_t)MS_ * 4);
+    hs_ = dmalloc((size_t)MS_ * Wld_ * es_); d_out_ids_ = (int32_t*)dmalloc((size_t)MS_ * 4);
+    logits_ = (float*)dmalloc((size_t)opt.max_batch * V * 4);      // own logits: sampling steps only (one row per sequence)
     cuda_check(cudaMallocHost(&h_out_ids, (size_t)MS_ * 4), "cudaMallocHost");
     mask_words = (V + 31) / 32; mask_slots = 0; max_mask_updates = 0;       // grammar-constrained sampling is not wired to this family's head
 
