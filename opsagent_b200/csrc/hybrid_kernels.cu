@@ -211,7 +211,7 @@ constexpr int MLA_MQ = 64;
 template <int NVB, int MLA_KT>      // MLA_KT = cache rows per tile: 32, or 16 where that lets two CTAs share an SM
 __global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn a, const float* __restrict__ q_abs, const __nv_bfloat16* __restrict__ cache,
                                                                    __nv_bfloat16* __restrict__ lat_out, HyRows r, const int32_t* __restrict__ tile_seq,
-                                                                   const int32_t* __restrict__ tile_q0) {
+                                                                   const int32_t* __restrict__ tile_q0, HyMlaSplit sp) {
     HY_PDL();
     extern __shared__ __align__(16) uint8_t mla_smem[];
     const int R = a.kv_rank, E = R + a.rot_dim, EP = E + 8, H = a.heads;
@@ -230,8 +230,11 @@ __global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn 
         *reinterpret_cast<uint32_t*>(Qs + qi * EP + e) = pack_bf16x2(v.x * qscale, v.y * qscale);
     }
     for (int qi = tid; qi < MLA_MQ; qi += 128) qpos[qi] = qi < nq ? r.positions[row0 + (q0 + qi) / H] : 0;
-    const int max_pos = r.positions[row0 + (q0 + nq - 1) / H];
-    const int n_kt = max_pos / MLA_KT + 1;
+    // a decoding row's keys may be cut into parts (one CTA each): this CTA walks cache rows [k0, k1) and leaves an unnormalised partial
+    const int k0 = sp.tile_k0 ? sp.tile_k0[blockIdx.x] : 0, k1 = sp.tile_k0 ? sp.tile_k1[blockIdx.x] : 0, slot = sp.tile_k0 ? sp.tile_slot[blockIdx.x] : -1;
+    int max_pos = r.positions[row0 + (q0 + nq - 1) / H];
+    if (k1 > 0 && k1 - 1 < max_pos) max_pos = k1 - 1;
+    const int kt0 = k0 / MLA_KT, n_kt = max_pos / MLA_KT + 1;
     const int32_t* bt = r.block_tables + (long long)seq * r.max_pages_per_seq;
     auto load_tile = [&](int kt, int buf) {
         const int chunks = E / 8;
@@ -248,13 +251,13 @@ __global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn 
     for (int i = 0; i < NVB; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
     const bool active = 16 * warp < nq;
-    load_tile(0, 0);
-    for (int kt = 0; kt < n_kt; ++kt) {
-        if (kt + 1 < n_kt) { load_tile(kt + 1, (kt + 1) & 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+    load_tile(kt0, 0);
+    for (int kt = kt0; kt < n_kt; ++kt) {
+        if (kt + 1 < n_kt) { load_tile(kt + 1, (kt + 1 - kt0) & 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
         else asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
         if (active) {
-            const __nv_bfloat16* Kb = Ks + (kt & 1) * MLA_KT * EP;
+            const __nv_bfloat16* Kb = Ks + ((kt - kt0) & 1) * MLA_KT * EP;
             constexpr int NB = MLA_KT / 8;
             float s[NB][4];
 #pragma unroll
@@ -283,7 +286,7 @@ __global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn 
                 }
             mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1)); mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
             mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)); mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-            const float n_lo = fmaxf(m_lo, mx_lo), n_hi = fmaxf(m_hi, mx_hi);       // finite: key 0 is visible to every query and lies in tile 0
+            const float n_lo = fmaxf(m_lo, mx_lo), n_hi = fmaxf(m_hi, mx_hi);       // finite: the first row of a CTA's range is visible to each of its queries
             const float c_lo = exp2f(m_lo - n_lo), c_hi = exp2f(m_hi - n_hi);
             m_lo = n_lo; m_hi = n_hi;
             float sum_lo = 0.f, sum_hi = 0.f;
@@ -313,8 +316,20 @@ __global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn 
     if (!active) return;
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-    const float i_lo = 1.0f / l_lo, i_hi = 1.0f / l_hi;
     const int q_lo = 16 * warp + (lane >> 2), q_hi = q_lo + 8;
+    if (slot >= 0) {                                  // partial: fp32 sums, running maximum (base-2 scores) and denominator per query
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int qi = half ? q_hi : q_lo;
+            if (qi >= nq) continue;
+            float* dst = sp.ws_o + ((long long)slot * H + qi) * R + vbase + (lane & 3) * 2;
+#pragma unroll
+            for (int nb = 0; nb < NVB; ++nb) *reinterpret_cast<float2*>(dst + nb * 8) = make_float2(o[nb][half * 2], o[nb][half * 2 + 1]);
+            if (blockIdx.y == 0 && (lane & 3) == 0) { sp.ws_ml[((long long)slot * H + qi) * 2] = half ? m_hi : m_lo; sp.ws_ml[((long long)slot * H + qi) * 2 + 1] = half ? l_hi : l_lo; }
+        }
+        return;
+    }
+    const float i_lo = 1.0f / l_lo, i_hi = 1.0f / l_hi;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const int qi = half ? q_hi : q_lo;
@@ -323,6 +338,23 @@ __global__ void __launch_bounds__(128) hy_mla_attention_mma_kernel(HyLatentAttn 
         __nv_bfloat16* dst = lat_out + ((long long)row * H + h) * R + vbase + (lane & 3) * 2;
 #pragma unroll
         for (int nb = 0; nb < NVB; ++nb) *reinterpret_cast<uint32_t*>(dst + nb * 8) = pack_bf16x2(o[nb][half * 2] * inv, o[nb][half * 2 + 1] * inv);
+    }
+}
+
+// joins the parts of a decoding row: out = sum_p 2^(m_p - M) O_p / sum_p 2^(m_p - M) l_p, parts in order
+__global__ void __launch_bounds__(128) hy_mla_merge_kernel(const int32_t* item_row, const int32_t* item_slot0, const int32_t* item_parts, const float* ws_o,
+                                                           const float* ws_ml, __nv_bfloat16* lat_out, int H, int R) {
+    HY_PDL();
+    const int row = item_row[blockIdx.x], slot0 = item_slot0[blockIdx.x], P = item_parts[blockIdx.x], h = blockIdx.y;
+    float M = -INFINITY;
+    for (int p = 0; p < P; ++p) M = fmaxf(M, ws_ml[((long long)(slot0 + p) * H + h) * 2]);
+    float L = 0.f;
+    for (int p = 0; p < P; ++p) { const float* ml = ws_ml + ((long long)(slot0 + p) * H + h) * 2; L += exp2f(ml[0] - M) * ml[1]; }
+    const float inv = 1.0f / L;
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+        float acc = 0.f;
+        for (int p = 0; p < P; ++p) acc += exp2f(ws_ml[((long long)(slot0 + p) * H + h) * 2] - M) * ws_o[((long long)(slot0 + p) * H + h) * R + c];
+        lat_out[((long long)row * H + h) * R + c] = __float2bfloat16_rn(acc * inv);
     }
 }
 
@@ -812,22 +844,27 @@ static int mla_mma_nvb(const HyLatentAttn& a) {
 bool hy_mla_mma_supported(const HyLatentAttn& a) { return mla_mma_nvb(a) != 0; }
 template <int NVB, int KT>
 static cudaError_t mla_mma_launch(const HyLatentAttn& a, const float* q_abs, const void* cache, void* lat_out, const HyRows& r, const int32_t* tile_seq,
-                                  const int32_t* tile_q0, int n_tiles, cudaStream_t s) {
+                                  const int32_t* tile_q0, int n_tiles, const HyMlaSplit& sp, cudaStream_t s) {
     static bool done[16] = {};
     cudaError_t e = ensure_dynamic_smem(hy_mla_attention_mma_kernel<NVB, KT>, 200 * 1024, done);      // set once per device: the most any size asks for
     if (e != cudaSuccess) return e;
     dim3 grid(n_tiles, a.kv_rank / (NVB * 8));
     return launch_plain(hy_mla_attention_mma_kernel<NVB, KT>, grid, dim3(128), mla_mma_smem(a.kv_rank + a.rot_dim, KT), s, a, q_abs, (const bf*)cache, (bf*)lat_out, r,
-                        tile_seq, tile_q0);
+                        tile_seq, tile_q0, sp);
+}
+cudaError_t hy_mla_merge(const int32_t* item_row, const int32_t* item_slot0, const int32_t* item_parts, int n_items, const float* ws_o, const float* ws_ml, void* lat_out,
+                         int heads, int kv_rank, cudaStream_t s) {
+    if (n_items <= 0) return cudaSuccess;
+    return launch_plain(hy_mla_merge_kernel, dim3(n_items, heads), dim3(128), 0, s, item_row, item_slot0, item_parts, ws_o, ws_ml, (bf*)lat_out, heads, kv_rank);
 }
 cudaError_t hy_mla_attention_mma(const HyLatentAttn& a, const float* q_abs, const void* cache, void* lat_out, const HyRows& r, const int32_t* tile_seq,
-                                 const int32_t* tile_q0, int n_tiles, cudaStream_t s) {
+                                 const int32_t* tile_q0, int n_tiles, const HyMlaSplit& sp, cudaStream_t s) {
     const int nvb = mla_mma_nvb(a), E = a.kv_rank + a.rot_dim;
     if (!nvb) return cudaErrorInvalidValue;
     // 32-row tiles when two CTAs (8 warps) still fit an SM's shared memory or nothing smaller would make them fit; else 16-row tiles
     // (a step with few tiles — decoding — is a latency chain per CTA: the larger tile halves its length)
     const bool kt32 = mla_mma_smem(E, 32) <= 113 * 1024 || mla_mma_smem(E, 16) > 113 * 1024 || n_tiles * (a.kv_rank / (nvb * 8)) < 296;
-#define HY_MLA(NVB) (kt32 ? mla_mma_launch<NVB, 32>(a, q_abs, cache, lat_out, r, tile_seq, tile_q0, n_tiles, s) : mla_mma_launch<NVB, 16>(a, q_abs, cache, lat_out, r, tile_seq, tile_q0, n_tiles, s))
+#define HY_MLA(NVB) (kt32 ? mla_mma_launch<NVB, 32>(a, q_abs, cache, lat_out, r, tile_seq, tile_q0, n_tiles, sp, s) : mla_mma_launch<NVB, 16>(a, q_abs, cache, lat_out, r, tile_seq, tile_q0, n_tiles, sp, s))
     return nvb == 32 ? HY_MLA(32) : nvb == 16 ? HY_MLA(16) : HY_MLA(8);
 #undef HY_MLA
 }

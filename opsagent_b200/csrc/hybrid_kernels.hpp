@@ -48,10 +48,16 @@ cudaError_t hy_mla_attention(bool f32, const HyLatentAttn& a, const float* q_abs
 
 // the same on the tensor cores (bf16 only; sizes: kv_rank a multiple of 64, kv_rank + rot_dim of 16).  A tile = 64 consecutive (row, head)
 // pairs of one sequence starting at pair tile_q0 of sequence tile_seq; the host lists the tiles of a step.
+// Decoding rows with long contexts: a tile may cover only the cache rows [tile_k0, tile_k1) (multiples of 32; k1 = 0: to the query's position)
+// and then leaves its fp32 partial (sums, running maximum, denominator) in workspace slot tile_slot (-1: final result); hy_mla_merge joins the
+// parts of a row in order.  How a row is cut depends on its own position only, never on the rest of the step.
 constexpr int HY_MLA_TILE_QUERIES = 64;
+struct HyMlaSplit { const int32_t* tile_k0; const int32_t* tile_k1; const int32_t* tile_slot; float* ws_o; float* ws_ml; };   // tile_k0 == null: no tile is cut
 bool hy_mla_mma_supported(const HyLatentAttn& a);
 cudaError_t hy_mla_attention_mma(const HyLatentAttn& a, const float* q_abs, const void* cache, void* lat_out, const HyRows& r, const int32_t* tile_seq,
-                                 const int32_t* tile_q0, int n_tiles, cudaStream_t s);
+                                 const int32_t* tile_q0, int n_tiles, const HyMlaSplit& sp, cudaStream_t s);
+cudaError_t hy_mla_merge(const int32_t* item_row, const int32_t* item_slot0, const int32_t* item_parts, int n_items, const float* ws_o, const float* ws_ml, void* lat_out,
+                         int heads, int kv_rank, cudaStream_t s);
 
 // y = silu(causal conv over time of `in` per channel (+ bias)); inputs before a sequence's first row of this step come from its tail
 // (the last taps-1 inputs of earlier steps; zeros at the start of a sequence).  hy_conv_tails then stores the new tails.

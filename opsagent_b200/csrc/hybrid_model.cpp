@@ -136,7 +136,7 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
     final_norm_ = upload_f32(vec("final.norm", W, 1.f, 0.1f));
     if (hc_.loop_times > 0) { loop_in_ = upload_mat(tensor("loop.in", W, 2 * W)); loop_step_ = upload_f32(vec("loop.step", hc_.loop_times * W, 0.f, 0.1f)); }
     lw_.resize(hc_.layers.size());
-    int max_in = 8, max_p2 = 8, max_conv = 8, max_mix = 8, max_qabs = 8, max_lat = 8, max_qk = 8, max_v = 8, max_dec = 8, max_h = 8, max_act = 8, max_top = 1, max_E = 1, max_ffp = 16;
+    int max_in = 8, max_p2 = 8, max_conv = 8, max_mix = 8, max_qabs = 8, max_lat = 8, max_qk = 8, max_v = 8, max_dec = 8, max_h = 8, max_act = 8, max_top = 1, max_E = 1, max_ffp = 16, max_lat_heads = 1;
     for (size_t li = 0; li < hc_.layers.size(); ++li) {
         const HyLayer& l = hc_.layers[li]; LayerW& w = lw_[li];
         const std::string p = "l" + std::to_string(li) + ".", mx = p + "mix.";
@@ -178,7 +178,7 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
                 }
                 rt.cos = upload_f32(cs); rt.sin = upload_f32(sn); w.rope = (int)ropes_.size(); ropes_.push_back(rt);
             }
-            max_qabs = std::max(max_qabs, l.heads * E); max_lat = std::max(max_lat, l.heads * l.kv_rank); max_mix = std::max(max_mix, l.heads * l.vdim);
+            max_lat_heads = std::max(max_lat_heads, l.heads); max_qabs = std::max(max_qabs, l.heads * E); max_lat = std::max(max_lat, l.heads * l.kv_rank); max_mix = std::max(max_mix, l.heads * l.vdim);
         } else if (l.type == HY_CHANNEL_DELTA) {
             const int qk = l.kv_heads * l.dim, vd = l.heads * l.vdim;
             append_rows(in.v, rows, W, tensor(mx + "q", qk, W).v, qk, 1); append_rows(in.v, rows, W, tensor(mx + "k", qk, W).v, qk, 1);
@@ -294,7 +294,9 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
         }
     }
     meta_cap_words_ = 4 * MR + (size_t)MS_ + (size_t)opt.max_batch * (max_pages_per_seq + 8) + 64;
-    for (const HyLayer& l : hc_.layers) if (l.type == HY_LATENT_ATTENTION) meta_cap_words_ += 2 * (MR * l.heads / HY_MLA_TILE_QUERIES + (size_t)opt.max_batch + 8);
+    split_slots_ = std::min(16 * opt.max_batch, 4096);
+    for (const HyLayer& l : hc_.layers) if (l.type == HY_LATENT_ATTENTION) meta_cap_words_ += 5 * (MR * l.heads / HY_MLA_TILE_QUERIES + (size_t)opt.max_batch + (size_t)split_slots_ + 8) + 3 * ((size_t)opt.max_batch + 4);
+    if (hc_.n_caches > 0 && !f32_) { split_o_ = (float*)dmalloc((size_t)split_slots_ * max_lat * 4); split_ml_ = (float*)dmalloc((size_t)split_slots_ * max_lat_heads * 2 * 4); }
     for (int i = 0; i < 2; ++i) {
         cuda_check(cudaMallocHost(&h_meta_buf_[i], meta_cap_words_ * 4), "cudaMallocHost meta");
         cuda_check(cudaEventCreateWithFlags(&meta_ev_[i], cudaEventDisableTiming), "cudaEventCreate meta");
@@ -399,19 +401,35 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
     const size_t o_bt = put(in.block_tables.data(), in.block_tables.size()), o_rs = put(row_seq_.data(), T), o_r0 = put(in.seq_row0.data(), S + 1);
     const size_t o_p0 = put(seq_pos0_.data(), S), o_st = put(in.state_slots.data(), S);
     // tensor-core attention: tiles of 64 consecutive (row, head) pairs of one sequence, listed once per distinct head count
-    struct TileList { int heads; size_t o_seq, o_q0; int n; };
+    struct TileList { int heads; size_t o_seq, o_q0, o_k0, o_k1, o_slot, o_mrow, o_mslot, o_mparts; int n, n_merge; };
     std::vector<TileList> tile_lists;
     if (!f32_ && opt.hy_tensor_core)
         for (const HyLayer& l : hc_.layers) {
             if (l.type != HY_LATENT_ATTENTION || !hy_mla_mma_supported(HyLatentAttn{l.heads, l.dim, l.rot_dim, l.vdim, l.kv_rank, l.rot_dims, l.scale})) continue;
             bool have = false; for (const TileList& tl : tile_lists) have |= tl.heads == l.heads;
             if (have) continue;
-            tile_seq_.clear(); tile_q0_.clear();
+            tile_seq_.clear(); tile_q0_.clear(); tile_k0_.clear(); tile_k1_.clear(); tile_slot_.clear(); merge_row_.clear(); merge_slot_.clear(); merge_parts_.clear();
+            int next_slot = 0;
             for (int sq = 0; sq < S; ++sq) {
-                const int nq = (in.seq_row0[sq + 1] - in.seq_row0[sq]) * l.heads;
-                for (int q0 = 0; q0 < nq; q0 += HY_MLA_TILE_QUERIES) { tile_seq_.push_back(sq); tile_q0_.push_back(q0); }
+                const int len = in.seq_row0[sq + 1] - in.seq_row0[sq], nq = len * l.heads, ctx = seq_pos0_[sq] + 1;
+                // a decoding row with a long context: its cache rows in 2..16 parts of >= 256 rows, one CTA each, joined afterwards.  The cut
+                // depends on the row's position only.
+                int parts = (len == 1 && nq <= HY_MLA_TILE_QUERIES) ? std::min(16, ctx / 256) : 1;
+                if (parts > 1 && next_slot + parts > split_slots_) parts = 1;
+                if (parts > 1) {
+                    const int per = ((ctx + parts - 1) / parts + 31) / 32 * 32; parts = (ctx + per - 1) / per;
+                    merge_row_.push_back(in.seq_row0[sq]); merge_slot_.push_back(next_slot); merge_parts_.push_back(parts);
+                    for (int pz = 0; pz < parts; ++pz) {
+                        tile_seq_.push_back(sq); tile_q0_.push_back(0); tile_k0_.push_back(pz * per); tile_k1_.push_back(std::min(ctx, (pz + 1) * per)); tile_slot_.push_back(next_slot++);
+                    }
+                    continue;
+                }
+                for (int q0 = 0; q0 < nq; q0 += HY_MLA_TILE_QUERIES) { tile_seq_.push_back(sq); tile_q0_.push_back(q0); tile_k0_.push_back(0); tile_k1_.push_back(0); tile_slot_.push_back(-1); }
             }
-            TileList tl; tl.heads = l.heads; tl.n = (int)tile_seq_.size(); tl.o_seq = put(tile_seq_.data(), tile_seq_.size()); tl.o_q0 = put(tile_q0_.data(), tile_q0_.size());
+            TileList tl; tl.heads = l.heads; tl.n = (int)tile_seq_.size(); tl.n_merge = (int)merge_row_.size();
+            tl.o_seq = put(tile_seq_.data(), tile_seq_.size()); tl.o_q0 = put(tile_q0_.data(), tile_q0_.size());
+            tl.o_k0 = put(tile_k0_.data(), tile_k0_.size()); tl.o_k1 = put(tile_k1_.data(), tile_k1_.size()); tl.o_slot = put(tile_slot_.data(), tile_slot_.size());
+            tl.o_mrow = put(merge_row_.data(), merge_row_.size()); tl.o_mslot = put(merge_slot_.data(), merge_slot_.size()); tl.o_mparts = put(merge_parts_.data(), merge_parts_.size());
             tile_lists.push_back(tl);
         }
     cuda_check(cudaMemcpyAsync(d_meta_, hm, wd * 4, cudaMemcpyHostToDevice, stream), "meta H2D");
@@ -453,7 +471,12 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
             cuda_check(hy_mla_prep(f32_, a, at(proj_, w.off_a), ld_proj_, at(proj_, w.off_b), ld_proj_, w.dkv_norm, hc_.eps, ropes_[w.rope].cos, ropes_[w.rope].sin,
                                    caches_[run.cache_idx], q_abs_, r, stream), "latent cache write"); MARK(4);
             const TileList* tl = nullptr; for (const TileList& t : tile_lists) if (t.heads == l.heads && hy_mla_mma_supported(a)) tl = &t;
-            if (tl) cuda_check(hy_mla_attention_mma(a, q_abs_, caches_[run.cache_idx], lat_, r, d_meta_ + tl->o_seq, d_meta_ + tl->o_q0, tl->n, stream), "latent attention (mma)");
+            if (tl) {
+                HyMlaSplit sp{nullptr, nullptr, nullptr, split_o_, split_ml_};
+                if (tl->n_merge > 0) { sp.tile_k0 = d_meta_ + tl->o_k0; sp.tile_k1 = d_meta_ + tl->o_k1; sp.tile_slot = d_meta_ + tl->o_slot; }
+                cuda_check(hy_mla_attention_mma(a, q_abs_, caches_[run.cache_idx], lat_, r, d_meta_ + tl->o_seq, d_meta_ + tl->o_q0, tl->n, sp, stream), "latent attention (mma)");
+                cuda_check(hy_mla_merge(d_meta_ + tl->o_mrow, d_meta_ + tl->o_mslot, d_meta_ + tl->o_mparts, tl->n_merge, split_o_, split_ml_, lat_, l.heads, l.kv_rank, stream), "latent attention (join)");
+            }
             else cuda_check(hy_mla_attention(f32_, a, q_abs_, caches_[run.cache_idx], lat_, r, stream), "latent attention");
             MARK(5);
             if (head_tc) for (int hd = 0; hd < l.heads; ++hd) gemm(HY_STORE, at(lat_, (size_t)hd * l.kv_rank), l.heads * l.kv_rank, w.uv_heads[hd], at(mix_, (size_t)hd * l.vdim), ld_mix_, T, nullptr, 1.f);

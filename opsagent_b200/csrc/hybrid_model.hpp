@@ -67,7 +67,8 @@ private:
     int32_t *idx_ = nullptr, *d_out_ids_ = nullptr, *tile_expert_ = nullptr, *row_src_ = nullptr, *n_tiles_ = nullptr, *dst_of_ = nullptr; int max_tiles_ = 0;
     int32_t* h_meta_buf_[2] = {nullptr, nullptr}; cudaEvent_t meta_ev_[2] = {nullptr, nullptr}; int meta_idx_ = 0;
     int32_t* d_meta_ = nullptr; size_t meta_cap_words_ = 0;
-    std::vector<int32_t> row_seq_, seq_pos0_, tile_seq_, tile_q0_;
+    std::vector<int32_t> row_seq_, seq_pos0_, tile_seq_, tile_q0_, tile_k0_, tile_k1_, tile_slot_, merge_row_, merge_slot_, merge_parts_;
+    float *split_o_ = nullptr, *split_ml_ = nullptr; int split_slots_ = 0;       // partials of decoding rows whose cache rows are cut into parts
 };
 
 }  // namespace oa

@@ -180,22 +180,22 @@ def test_bf16_tensor_core_path_and_plain_path_agree_with_the_oracle(tmp_path):
 def test_tensor_core_attention_sizes(tmp_path):
     """Latent sizes that take the mma.sync attention kernel (rank a multiple of 64, rank + rotated a multiple of 16) and, for prompts of 256
     rows and more, the per-head tensor-core absorption / up-projection products: whole prompts, portions that straddle the 64-query tiles and
-    the 16- or 32-row cache tiles, and decoding, against the oracle and against the plain kernels (hy_tensor_core = 0)."""
+    the 16- or 32-row cache tiles, and decoding (also with the cache rows of a row cut into parts), against the oracle and against the plain kernels (hy_tensor_core = 0)."""
     layers = [O.attention_layer(heads=4, dim=16, rot_dim=16, vdim=16, kv_rank=64), O.attention_layer(heads=3, dim=24, rot_dim=32, vdim=8, kv_rank=128, base=500.0)]
     cfg = O.make_config(layers, width=64, vocab=96)
     W = checkpoint(tmp_path, cfg, seed=13, sharp=3.0)
-    toks = tokens_of(cfg, 300, 9)
+    toks = tokens_of(cfg, 600, 9)
     want = O.forward(cfg, W, toks)
     outs = {}
     for tc in (1, 0):
-        with engine(tmp_path, "bfloat16", hy_tensor_core=tc) as eng:
-            outs[tc] = [replay(eng, 1, toks, [300]), replay(eng, 2, toks, [17, 33, 63, 130, 41]), replay(eng, 3, toks, [270])]
+        with engine(tmp_path, "bfloat16", pages=10, hy_tensor_core=tc) as eng:     # the last tokens decode one by one at contexts past 512: their cache rows are cut into parts
+            outs[tc] = [replay(eng, 1, toks, [600]), replay(eng, 2, toks, [17, 33, 63, 130, 41, 290]), replay(eng, 3, toks, [500])]
     for tc in (1, 0):
         for got in outs[tc]:
             e = O.rel_err(got.astype(np.float64), want)
             assert np.quantile(e, 0.95) < 0.06 and e.max() < 0.2, f"tensor cores {tc}: 95% {np.quantile(e, 0.95):.3e}, worst {e.max():.3e}"
-    for got in outs[1][1:]:                           # schedules agree far more closely than bf16 agrees with the oracle
-        assert O.rel_err(got.astype(np.float64), outs[1][0].astype(np.float64)).max() < SAME_TOL
+    for got in outs[1][1:]:                           # schedules agree more closely than bf16 agrees with the oracle (a cut row sums its parts
+        assert O.rel_err(got.astype(np.float64), outs[1][0].astype(np.float64)).max() < 3 * SAME_TOL      # in another order, and these scores are sharp)
 
 
 def test_greedy_generation_through_the_scheduler(tmp_path):
