@@ -111,6 +111,30 @@ __global__ void hy_concat_kernel(const float* x, const float* x0, TA* cat, int T
     const int t = blockIdx.x;
     for (int c = threadIdx.x; c < W; c += blockDim.x) { stf(cat + (long long)t * 2 * W + c, x[(long long)t * W + c]); stf(cat + (long long)t * 2 * W + W + c, x0[(long long)t * W + c]); }
 }
+// one read of the row: W <= 8192, a multiple of 4; each thread keeps up to 8 float4 of it
+template <typename TA>
+__global__ void __launch_bounds__(256) hy_layernorm_reg_kernel(const float* x, const int32_t* rows, const float* w, TA* out, int ldo, int W, float eps) {
+    HY_PDL();
+    __shared__ float red[32];
+    const int t = blockIdx.x; const float4* xr = reinterpret_cast<const float4*>(x + (long long)(rows ? rows[t] : t) * W);
+    const int n4 = W / 4;
+    float4 v[8]; float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { const int i = threadIdx.x + k * 256; if (i < n4) { v[k] = xr[i]; s += (v[k].x + v[k].y) + (v[k].z + v[k].w); } }
+    const float mean = block_sum(s, red) / (float)W;
+    float q = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { const int i = threadIdx.x + k * 256; if (i < n4) { const float a = v[k].x - mean, b = v[k].y - mean, c = v[k].z - mean, d = v[k].w - mean; q += (a * a + b * b) + (c * c + d * d); } }
+    const float rstd = 1.0f / sqrtf(block_sum(q, red) / (float)W + eps);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int i = threadIdx.x + k * 256;
+        if (i < n4) {
+            const float4 g = reinterpret_cast<const float4*>(w)[i]; TA* o = out + (long long)t * ldo + 4 * i;
+            stf(o, (v[k].x - mean) * rstd * g.x); stf(o + 1, (v[k].y - mean) * rstd * g.y); stf(o + 2, (v[k].z - mean) * rstd * g.z); stf(o + 3, (v[k].w - mean) * rstd * g.w);
+        }
+    }
+}
 template <typename TA>
 __global__ void __launch_bounds__(256) hy_layernorm_kernel(const float* x, const int32_t* rows, const float* w, TA* out, int ldo, int W, float eps) {
     HY_PDL();
@@ -820,6 +844,9 @@ cudaError_t hy_concat(bool f32, const float* x, const float* x0, void* cat, int 
 }
 cudaError_t hy_layernorm(bool f32, const float* x, const int32_t* rows, const float* w, void* out, int ldo, int T, int W, float eps, cudaStream_t s) {
     if (T <= 0) return cudaSuccess;
+    if (W % 4 == 0 && W <= 8192 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0)
+        return f32 ? launch_plain(hy_layernorm_reg_kernel<float>, dim3(T), dim3(256), 0, s, x, rows, w, (float*)out, ldo, W, eps)
+                   : launch_plain(hy_layernorm_reg_kernel<bf>, dim3(T), dim3(256), 0, s, x, rows, w, (bf*)out, ldo, W, eps);
     return f32 ? launch_plain(hy_layernorm_kernel<float>, dim3(T), dim3(256), 0, s, x, rows, w, (float*)out, ldo, W, eps)
                : launch_plain(hy_layernorm_kernel<bf>, dim3(T), dim3(256), 0, s, x, rows, w, (bf*)out, ldo, W, eps);
 }

@@ -177,6 +177,23 @@ def test_bf16_tensor_core_path_and_plain_path_agree_with_the_oracle(tmp_path):
             check(replay(eng, 2, toks, [130]), want, "bfloat16")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_fit_no_tile(tmp_path, dtype):
+    """Widths, ranks and head sizes that are multiples of nothing: every product falls back to the plain GEMM, attention to the one-query
+    kernel, the recurrences to the shared-memory kernel; one-tap and five-tap convolutions; one expert group; a single chosen expert."""
+    layers = [O.attention_layer(heads=3, dim=6, rot_dim=4, vdim=10, kv_rank=20, mlp=O.moe(experts=3, top=1, groups=1, keep=1, ff=10, scale=0.7)),
+              O.delta_layer(heads=3, kv_heads=3, dim=6, vdim=10, conv=1, mlp=None),
+              O.mamba_layer(heads=2, vdim=6, state=6, groups=2, norm_groups=2, conv=5, mlp=O.moe(experts=6, top=3, groups=2, keep=2, ff=21, scale=1.0)),
+              O.delta_layer(heads=4, kv_heads=2, dim=132, vdim=12, conv=3, mlp=None)]          # dim beyond the register kernel
+    cfg = O.make_config(layers, width=36, vocab=51, loop={"start": 1, "stop": 3, "times": 2}, logit_scale=0.5)
+    W = checkpoint(tmp_path, cfg, seed=21, low_rank=5)
+    toks = tokens_of(cfg, 90, 11)
+    want = O.forward(cfg, W, toks)
+    with engine(tmp_path, dtype) as eng:
+        check(replay(eng, 1, toks, [90]), want, dtype)
+        check(replay(eng, 2, toks, [2, 62, 3, 20]), want, dtype)
+
+
 def test_tensor_core_attention_sizes(tmp_path):
     """Latent sizes that take the mma.sync attention kernel (rank a multiple of 64, rank + rotated a multiple of 16) and, for prompts of 256
     rows and more, the per-head tensor-core absorption / up-projection products: whole prompts, portions that straddle the 64-query tiles and
