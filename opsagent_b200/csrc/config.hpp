@@ -118,6 +118,7 @@ struct EngineOptions {
     std::string model_dir;        // checkpoint folder (config.json + model.safetensors): the model class is chosen by config.json's "architecture"
     int f32 = 0;                  // "dtype": "float32" — everything in fp32 (hybrid family only); default bf16 matrices and activations with fp32 accumulation
     int hy_moe_grouped_rows = 8;  // hybrid family, bf16: batches of at least this many rows run the routed experts as grouped tensor-core products (rows sorted by expert); smaller ones one (token, choice) at a time
+    int hy_unabsorbed_rows = 64;  // hybrid family, bf16: a sequence that brings at least this many rows to a step runs latent attention in its prefill form (keys / values of its context up-projected by a GEMM, multi-head attention); fewer rows (decoding): the absorbed form over the latent cache.  0 = always absorbed
     int hy_tensor_core = 1;       // hybrid family, bf16: projections and grouped expert products on the tcgen05 GEMM (0: the plain FMA kernels everywhere)
     std::string model_aliases;    // other model names this engine answers to, comma separated ("*" = any): the reference sends currentModel or "gpt-4" (execute.go:168-171)
     std::string weights;          // path of a Hugging Face *.safetensors file or shard directory (empty: seeded random init)

@@ -383,6 +383,151 @@ __global__ void __launch_bounds__(128) hy_mla_merge_kernel(const int32_t* item_r
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------------
+// prefill form of latent attention: per-head keys [W_uk c | rotated shared part] and values W_uv c of a sequence's whole context are first
+// materialised by one GEMM over its gathered cache rows (hy_gather_ctx + the tcgen05 GEMM); then this kernel runs ordinary causal
+// multi-head attention on them — 64 query rows of one (sequence, head) per CTA, 32-row key / value tiles through a cp.async double buffer,
+// S = Q K^T over dim + rot_dim and O += P V over vdim on mma.sync, online softmax in fp32 — and writes the heads' outputs straight into
+// the output projection's input.  Per key it costs dim + rot_dim + vdim multiply-adds instead of the absorbed form's 2 kv_rank + rot_dim.
+// ---------------------------------------------------------------------------------------------------------------------------------
+template <int NVB>
+__global__ void __launch_bounds__(128) hy_mha_prefill_mma_kernel(HyLatentAttn a, const __nv_bfloat16* __restrict__ q, int ldq, const float* __restrict__ q_abs,
+                                                                 const __nv_bfloat16* __restrict__ kv_ctx, int ld_kv, const __nv_bfloat16* __restrict__ lat_ctx,
+                                                                 __nv_bfloat16* __restrict__ mix, int ld_mix, HyRows r, const int32_t* __restrict__ tile_seq,
+                                                                 const int32_t* __restrict__ tile_head, const int32_t* __restrict__ tile_row0,
+                                                                 const int32_t* __restrict__ seq_base) {
+    HY_PDL();
+    extern __shared__ __align__(16) uint8_t mha_smem[];
+    constexpr int KT = 32, VD = NVB * 8;
+    const int R = a.kv_rank, E = R + a.rot_dim, H = a.heads, DN = a.dim, DQ = a.dim + a.rot_dim, QP = DQ + 8, VP = VD + 8;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(mha_smem);      // [64][QP]
+    __nv_bfloat16* Ks = Qs + MLA_MQ * QP;                                // [2][KT][QP]
+    __nv_bfloat16* Vs = Ks + 2 * KT * QP;                                // [2][KT][VP]
+    int* qpos = reinterpret_cast<int*>(Vs + 2 * KT * VP);                // [64]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int seq = tile_seq[blockIdx.x], h = tile_head[blockIdx.x], qr0 = tile_row0[blockIdx.x];
+    const int row0 = r.seq_row0[seq] + qr0, nq = min(MLA_MQ, r.seq_row0[seq + 1] - row0);
+    const long long base = seq_base[seq];
+    const float qscale = a.scale * 1.4426950408889634f;
+    for (int idx = tid; idx < MLA_MQ * (DQ / 2); idx += 128) {
+        const int qi = idx / (DQ / 2), e = (idx - qi * (DQ / 2)) * 2;
+        uint32_t v = 0;
+        if (qi < nq) {
+            if (e < DN) v = *reinterpret_cast<const uint32_t*>(q + (long long)(row0 + qi) * ldq + h * DQ + e);
+            else { const float2 f = *reinterpret_cast<const float2*>(q_abs + ((long long)(row0 + qi) * H + h) * E + R + (e - DN)); v = pack_bf16x2(f.x, f.y); }
+        }
+        *reinterpret_cast<uint32_t*>(Qs + qi * QP + e) = v;
+    }
+    for (int qi = tid; qi < MLA_MQ; qi += 128) qpos[qi] = qi < nq ? r.positions[row0 + qi] : 0;
+    const int max_pos = r.positions[row0 + nq - 1];
+    const int n_kt = max_pos / KT + 1;
+    auto load_tile = [&](int kt, int buf) {
+        const int kc = DQ / 8, nc = DN / 8, vc = VD / 8;
+        for (int idx = tid; idx < KT * (kc + vc); idx += 128) {
+            const int j = idx / (kc + vc), c = idx - j * (kc + vc), key = kt * KT + j;
+            __nv_bfloat16* dst = c < kc ? Ks + (buf * KT + j) * QP + c * 8 : Vs + (buf * KT + j) * VP + (c - kc) * 8;
+            if (key <= max_pos) {
+                const __nv_bfloat16* src = c < nc ? kv_ctx + (base + key) * ld_kv + h * DN + c * 8
+                                         : c < kc ? lat_ctx + (base + key) * E + R + (c - nc) * 8
+                                                  : kv_ctx + (base + key) * ld_kv + H * DN + h * VD + (c - kc) * 8;
+                cp_async16(dst, src);
+            } else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float o[NVB][4];
+#pragma unroll
+    for (int i = 0; i < NVB; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    const bool active = 16 * warp < nq;
+    load_tile(0, 0);
+    for (int kt = 0; kt < n_kt; ++kt) {
+        if (kt + 1 < n_kt) { load_tile(kt + 1, (kt + 1) & 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        if (active) {
+            const __nv_bfloat16* Kb = Ks + (kt & 1) * KT * QP; const __nv_bfloat16* Vb = Vs + (kt & 1) * KT * VP;
+            float s[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+            const uint32_t qa = smem_u32(Qs + (16 * warp + (lane & 15)) * QP + (lane >> 4) * 8);
+            const uint32_t ka = smem_u32(Kb + ((lane >> 4) * 8 + (lane & 7)) * QP + ((lane >> 3) & 1) * 8);
+            for (int ks = 0; ks < DQ / 16; ++ks) {
+                uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                ldmatrix_x4(qa + ks * 32, a0, a1, a2, a3);
+                ldmatrix_x4(ka + ks * 32, b0, b1, b2, b3);
+                mma_bf16_16816(s[0], a0, a1, a2, a3, b0, b1); mma_bf16_16816(s[1], a0, a1, a2, a3, b2, b3);
+                ldmatrix_x4(ka + 16 * QP * 2 + ks * 32, b0, b1, b2, b3);
+                mma_bf16_16816(s[2], a0, a1, a2, a3, b0, b1); mma_bf16_16816(s[3], a0, a1, a2, a3, b2, b3);
+            }
+            const int p_lo = qpos[16 * warp + (lane >> 2)], p_hi = qpos[16 * warp + (lane >> 2) + 8];
+            float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+            for (int nb = 0; nb < 4; ++nb)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int key = kt * KT + nb * 8 + (lane & 3) * 2 + (c & 1);
+                    s[nb][c] = key > (c < 2 ? p_lo : p_hi) ? -INFINITY : s[nb][c] * qscale;
+                    if (c < 2) mx_lo = fmaxf(mx_lo, s[nb][c]); else mx_hi = fmaxf(mx_hi, s[nb][c]);
+                }
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1)); mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)); mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+            const float n_lo = fmaxf(m_lo, mx_lo), n_hi = fmaxf(m_hi, mx_hi);       // finite: key 0 is visible to every query and lies in tile 0
+            const float c_lo = exp2f(m_lo - n_lo), c_hi = exp2f(m_hi - n_hi);
+            m_lo = n_lo; m_hi = n_hi;
+            float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+            for (int nb = 0; nb < 4; ++nb) {
+                s[nb][0] = exp2f(s[nb][0] - n_lo); s[nb][1] = exp2f(s[nb][1] - n_lo); s[nb][2] = exp2f(s[nb][2] - n_hi); s[nb][3] = exp2f(s[nb][3] - n_hi);
+                sum_lo += s[nb][0] + s[nb][1]; sum_hi += s[nb][2] + s[nb][3];
+            }
+            l_lo = l_lo * c_lo + sum_lo; l_hi = l_hi * c_hi + sum_hi;
+#pragma unroll
+            for (int i = 0; i < NVB; ++i) { o[i][0] *= c_lo; o[i][1] *= c_lo; o[i][2] *= c_hi; o[i][3] *= c_hi; }
+            const uint32_t va = smem_u32(Vb + (((lane >> 3) & 1) * 8 + (lane & 7)) * VP + (lane >> 4) * 8);
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+                const uint32_t a0 = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]), a1 = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
+                const uint32_t a2 = pack_bf16x2(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = pack_bf16x2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int np = 0; np < NVB / 2; ++np) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(va + kk * 16 * VP * 2 + np * 32, b0, b1, b2, b3);
+                    mma_bf16_16816(o[2 * np], a0, a1, a2, a3, b0, b1); mma_bf16_16816(o[2 * np + 1], a0, a1, a2, a3, b2, b3);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (!active) return;
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    const float i_lo = 1.0f / l_lo, i_hi = 1.0f / l_hi;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int qi = 16 * warp + (lane >> 2) + half * 8;
+        if (qi >= nq) continue;
+        const float inv = half ? i_hi : i_lo;
+        __nv_bfloat16* dst = mix + (long long)(row0 + qi) * ld_mix + h * VD + (lane & 3) * 2;
+#pragma unroll
+        for (int nb = 0; nb < NVB; ++nb) *reinterpret_cast<uint32_t*>(dst + nb * 8) = pack_bf16x2(o[nb][half * 2] * inv, o[nb][half * 2 + 1] * inv);
+    }
+}
+// cache rows 0 .. ctx-1 of the listed sequences, contiguous: lat_ctx[seq_base[s] + j] = cache row j of sequence s (seq_base < 0: not listed)
+__global__ void __launch_bounds__(128) hy_gather_ctx_kernel(const __nv_bfloat16* __restrict__ cache, int E, const int32_t* __restrict__ block_tables, int mpps,
+                                                            const int32_t* __restrict__ seq_base, const int32_t* __restrict__ seq_row0, const int32_t* __restrict__ positions,
+                                                            __nv_bfloat16* __restrict__ lat_ctx) {
+    HY_PDL();
+    const int seq = blockIdx.x; const long long base = seq_base[seq];
+    if (base < 0) return;
+    const int ctx = positions[seq_row0[seq + 1] - 1] + 1, chunks = E / 8;
+    for (int idx = blockIdx.y * 16 * chunks + threadIdx.x; idx < min(ctx, (int)(blockIdx.y + 1) * 16) * chunks; idx += 128) {
+        const int j = idx / chunks, c = idx - j * chunks;
+        *reinterpret_cast<uint4*>(lat_ctx + (base + j) * E + c * 8) =
+            *reinterpret_cast<const uint4*>(cache + ((long long)block_tables[(long long)seq * mpps + (j >> 6)] * 64 + (j & 63)) * E + c * 8);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
 // short causal convolution with carried tails
 // ---------------------------------------------------------------------------------------------------------------------------------
 template <typename TA>
@@ -894,6 +1039,36 @@ cudaError_t hy_mla_attention_mma(const HyLatentAttn& a, const float* q_abs, cons
 #define HY_MLA(NVB) (kt32 ? mla_mma_launch<NVB, 32>(a, q_abs, cache, lat_out, r, tile_seq, tile_q0, n_tiles, sp, s) : mla_mma_launch<NVB, 16>(a, q_abs, cache, lat_out, r, tile_seq, tile_q0, n_tiles, sp, s))
     return nvb == 32 ? HY_MLA(32) : nvb == 16 ? HY_MLA(16) : HY_MLA(8);
 #undef HY_MLA
+}
+static int mha_nvb(const HyLatentAttn& a) {
+    if ((a.dim + a.rot_dim) % 16 != 0 || a.dim % 8 != 0 || a.rot_dim % 8 != 0 || a.kv_rank % 8 != 0) return 0;
+    return a.vdim == 128 ? 16 : a.vdim == 64 ? 8 : a.vdim == 32 ? 4 : a.vdim == 16 ? 2 : 0;
+}
+bool hy_mha_prefill_supported(const HyLatentAttn& a) { return mha_nvb(a) != 0 && a.dim + a.rot_dim <= 512; }
+cudaError_t hy_gather_ctx(const void* cache, int E, const HyRows& r, const int32_t* seq_base, int max_ctx, void* lat_ctx, cudaStream_t s) {
+    return launch_plain(hy_gather_ctx_kernel, dim3(r.S, (max_ctx + 15) / 16), dim3(128), 0, s, (const bf*)cache, E, r.block_tables, r.max_pages_per_seq, seq_base, r.seq_row0,
+                        r.positions, (bf*)lat_ctx);
+}
+template <int NVB>
+static cudaError_t mha_launch(const HyLatentAttn& a, const void* q, int ldq, const float* q_abs, const void* kv_ctx, int ld_kv, const void* lat_ctx, void* mix, int ld_mix,
+                              const HyRows& r, const int32_t* tile_seq, const int32_t* tile_head, const int32_t* tile_row0, const int32_t* seq_base, int n_tiles, cudaStream_t s) {
+    static bool done[16] = {};
+    cudaError_t e = ensure_dynamic_smem(hy_mha_prefill_mma_kernel<NVB>, 200 * 1024, done);
+    if (e != cudaSuccess) return e;
+    const size_t smem = (size_t)(MLA_MQ + 64) * (a.dim + a.rot_dim + 8) * 2 + (size_t)64 * (NVB * 8 + 8) * 2 + MLA_MQ * 4;
+    return launch_plain(hy_mha_prefill_mma_kernel<NVB>, dim3(n_tiles), dim3(128), smem, s, a, (const bf*)q, ldq, q_abs, (const bf*)kv_ctx, ld_kv, (const bf*)lat_ctx, (bf*)mix,
+                        ld_mix, r, tile_seq, tile_head, tile_row0, seq_base);
+}
+cudaError_t hy_mha_prefill(const HyLatentAttn& a, const void* q, int ldq, const float* q_abs, const void* kv_ctx, int ld_kv, const void* lat_ctx, void* mix, int ld_mix,
+                           const HyRows& r, const int32_t* tile_seq, const int32_t* tile_head, const int32_t* tile_row0, const int32_t* seq_base, int n_tiles, cudaStream_t s) {
+    if (n_tiles <= 0) return cudaSuccess;
+    switch (mha_nvb(a)) {
+        case 16: return mha_launch<16>(a, q, ldq, q_abs, kv_ctx, ld_kv, lat_ctx, mix, ld_mix, r, tile_seq, tile_head, tile_row0, seq_base, n_tiles, s);
+        case 8: return mha_launch<8>(a, q, ldq, q_abs, kv_ctx, ld_kv, lat_ctx, mix, ld_mix, r, tile_seq, tile_head, tile_row0, seq_base, n_tiles, s);
+        case 4: return mha_launch<4>(a, q, ldq, q_abs, kv_ctx, ld_kv, lat_ctx, mix, ld_mix, r, tile_seq, tile_head, tile_row0, seq_base, n_tiles, s);
+        case 2: return mha_launch<2>(a, q, ldq, q_abs, kv_ctx, ld_kv, lat_ctx, mix, ld_mix, r, tile_seq, tile_head, tile_row0, seq_base, n_tiles, s);
+    }
+    return cudaErrorInvalidValue;
 }
 cudaError_t hy_conv_silu(bool f32, const void* in, int ld_in, int C, const float* w, const float* bias, int taps, void* out, int ld_out, const void* tails, const HyRows& r,
                          cudaStream_t s) {

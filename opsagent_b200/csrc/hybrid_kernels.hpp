@@ -59,6 +59,16 @@ cudaError_t hy_mla_attention_mma(const HyLatentAttn& a, const float* q_abs, cons
 cudaError_t hy_mla_merge(const int32_t* item_row, const int32_t* item_slot0, const int32_t* item_parts, int n_items, const float* ws_o, const float* ws_ml, void* lat_out,
                          int heads, int kv_rank, cudaStream_t s);
 
+// Prefill form (bf16; dim and rot_dim multiples of 8, their sum of 16, vdim 16 / 32 / 64 / 128): hy_gather_ctx copies the cache rows 0..ctx-1 of
+// the sequences with seq_base[s] >= 0 to lat_ctx[seq_base[s] + j]; a GEMM makes kv_ctx = lat_ctx[:, :rank] . [W_uk ; W_uv]^T ([rows, heads dim |
+// heads vdim]); hy_mha_prefill then runs causal attention per (sequence, head) — a tile is 64 query rows starting at row tile_row0 of its
+// sequence — and writes mix[row, head * vdim ..].  Queries: unrotated part from q ([T, ldq], head by head [dim | rot_dim]), rotated part
+// from q_abs[.., rank:].
+bool hy_mha_prefill_supported(const HyLatentAttn& a);
+cudaError_t hy_gather_ctx(const void* cache, int E, const HyRows& r, const int32_t* seq_base, int max_ctx, void* lat_ctx, cudaStream_t s);
+cudaError_t hy_mha_prefill(const HyLatentAttn& a, const void* q, int ldq, const float* q_abs, const void* kv_ctx, int ld_kv, const void* lat_ctx, void* mix, int ld_mix,
+                           const HyRows& r, const int32_t* tile_seq, const int32_t* tile_head, const int32_t* tile_row0, const int32_t* seq_base, int n_tiles, cudaStream_t s);
+
 // y = silu(causal conv over time of `in` per channel (+ bias)); inputs before a sequence's first row of this step come from its tail
 // (the last taps-1 inputs of earlier steps; zeros at the start of a sequence).  hy_conv_tails then stores the new tails.
 cudaError_t hy_conv_silu(bool f32, const void* in, int ld_in, int C, const float* w, const float* bias, int taps, void* out, int ld_out,

@@ -136,7 +136,7 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
     final_norm_ = upload_f32(vec("final.norm", W, 1.f, 0.1f));
     if (hc_.loop_times > 0) { loop_in_ = upload_mat(tensor("loop.in", W, 2 * W)); loop_step_ = upload_f32(vec("loop.step", hc_.loop_times * W, 0.f, 0.1f)); }
     lw_.resize(hc_.layers.size());
-    int max_in = 8, max_p2 = 8, max_conv = 8, max_mix = 8, max_qabs = 8, max_lat = 8, max_qk = 8, max_v = 8, max_dec = 8, max_h = 8, max_act = 8, max_top = 1, max_E = 1, max_ffp = 16, max_lat_heads = 1;
+    int max_in = 8, max_p2 = 8, max_conv = 8, max_mix = 8, max_qabs = 8, max_lat = 8, max_qk = 8, max_v = 8, max_dec = 8, max_h = 8, max_act = 8, max_top = 1, max_E = 1, max_ffp = 16, max_lat_heads = 1, max_kv = 0, max_Eattn = 8;
     for (size_t li = 0; li < hc_.layers.size(); ++li) {
         const HyLayer& l = hc_.layers[li]; LayerW& w = lw_[li];
         const std::string p = "l" + std::to_string(li) + ".", mx = p + "mix.";
@@ -154,7 +154,13 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
             for (int h = 0; h < l.heads; ++h) for (int d = 0; d < l.dim; ++d) for (int r = 0; r < l.kv_rank; ++r)
                 ukt[((size_t)h * l.kv_rank + r) * l.dim + d] = uk.v[((size_t)h * l.dim + d) * l.kv_rank + r];
             w.uk_t = upload_act(ukt);
-            w.uv = upload_act(tensor(mx + "uv", l.heads * l.vdim, l.kv_rank).v);
+            HostMat uvm = tensor(mx + "uv", l.heads * l.vdim, l.kv_rank);
+            w.uv = upload_act(uvm.v);
+            if (!f32_ && opt.hy_tensor_core && opt.hy_unabsorbed_rows > 0 && hy_mha_prefill_supported(HyLatentAttn{l.heads, l.dim, l.rot_dim, l.vdim, l.kv_rank, l.rot_dims, l.scale})) {
+                HostMat kvu; kvu.N = l.heads * (l.dim + l.vdim); kvu.K = l.kv_rank; kvu.v = uk.v; kvu.v.insert(kvu.v.end(), uvm.v.begin(), uvm.v.end());
+                w.kv_up = upload_mat(kvu);       // [W_uk ; W_uv]: keys and values of a whole context in one product (prefill form)
+                max_kv = std::max(max_kv, up8(kvu.N));
+            }
             w.o = upload_mat(tensor(mx + "o", W, l.heads * l.vdim));
             if (!f32_ && opt.hy_tensor_core && l.dim % 8 == 0 && l.rot_dim % 8 == 0 && l.kv_rank % 8 == 0 && l.vdim % 8 == 0) {
                 const int bns[4] = {32, 64, 128, 256}; bool all = true;
@@ -178,7 +184,7 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
                 }
                 rt.cos = upload_f32(cs); rt.sin = upload_f32(sn); w.rope = (int)ropes_.size(); ropes_.push_back(rt);
             }
-            max_lat_heads = std::max(max_lat_heads, l.heads); max_qabs = std::max(max_qabs, l.heads * E); max_lat = std::max(max_lat, l.heads * l.kv_rank); max_mix = std::max(max_mix, l.heads * l.vdim);
+            max_Eattn = std::max(max_Eattn, E); max_lat_heads = std::max(max_lat_heads, l.heads); max_qabs = std::max(max_qabs, l.heads * E); max_lat = std::max(max_lat, l.heads * l.kv_rank); max_mix = std::max(max_mix, l.heads * l.vdim);
         } else if (l.type == HY_CHANNEL_DELTA) {
             const int qk = l.kv_heads * l.dim, vd = l.heads * l.vdim;
             append_rows(in.v, rows, W, tensor(mx + "q", qk, W).v, qk, 1); append_rows(in.v, rows, W, tensor(mx + "k", qk, W).v, qk, 1);
@@ -294,6 +300,9 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
         }
     }
     meta_cap_words_ = 4 * MR + (size_t)MS_ + (size_t)opt.max_batch * (max_pages_per_seq + 8) + 64;
+    ctx_cap_ = 2 * MR_;
+    if (max_kv > 0) { ld_kv_ = max_kv; lat_ctx_ = dmalloc((size_t)ctx_cap_ * max_Eattn * 2); kv_ctx_ = dmalloc((size_t)ctx_cap_ * ld_kv_ * 2); }
+    for (const HyLayer& l : hc_.layers) if (l.type == HY_LATENT_ATTENTION) meta_cap_words_ += 3 * ((MR / 64 + (size_t)opt.max_batch) * l.heads + 8) + (size_t)opt.max_batch + 8;
     split_slots_ = std::min(16 * opt.max_batch, 4096);
     for (const HyLayer& l : hc_.layers) if (l.type == HY_LATENT_ATTENTION) meta_cap_words_ += 5 * (MR * l.heads / HY_MLA_TILE_QUERIES + (size_t)opt.max_batch + (size_t)split_slots_ + 8) + 3 * ((size_t)opt.max_batch + 4);
     if (hc_.n_caches > 0 && !f32_) { split_o_ = (float*)dmalloc((size_t)split_slots_ * max_lat * 4); split_ml_ = (float*)dmalloc((size_t)split_slots_ * max_lat_heads * 2 * 4); }
@@ -373,7 +382,7 @@ void HybridModel::moe(const LayerW& w, const HyLayer& l, const HyRows& r, const 
 const char* HybridModel::kt_name(int id) const {
     static const char* n[32] = {"h2d+embed", "layer_norm", "in_proj_gemm", "latent_absorb+up_gemm", "latent_cache_write", "latent_attention", "conv", "recurrence_prep",
                                 "recurrence", "gated_norm", "low_rank_gemm", "out_proj_gemm", "router", "experts_per_token", "loop_in", "head+argmax",
-                                "expert_plan+gather", "expert_gate_up_gemm", "expert_down_gemm", "expert_combine", "", "", "", "", "", "", "", "", "", "", "", ""};
+                                "expert_plan+gather", "expert_gate_up_gemm", "expert_down_gemm", "expert_combine", "context_gather+kv_up_gemm", "attention_prefill_form", "", "", "", "", "", "", "", "", "", ""};
     return n[id & 31];
 }
 
@@ -400,38 +409,52 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
     const size_t o_tok = put(in.tokens.data(), T), o_pos = put(in.positions.data(), T), o_slot = put(in.slots.data(), T), o_samp = put(in.sample_rows.data(), NS);
     const size_t o_bt = put(in.block_tables.data(), in.block_tables.size()), o_rs = put(row_seq_.data(), T), o_r0 = put(in.seq_row0.data(), S + 1);
     const size_t o_p0 = put(seq_pos0_.data(), S), o_st = put(in.state_slots.data(), S);
-    // tensor-core attention: tiles of 64 consecutive (row, head) pairs of one sequence, listed once per distinct head count
-    struct TileList { int heads; size_t o_seq, o_q0, o_k0, o_k1, o_slot, o_mrow, o_mslot, o_mparts; int n, n_merge; };
-    std::vector<TileList> tile_lists;
-    if (!f32_ && opt.hy_tensor_core)
-        for (const HyLayer& l : hc_.layers) {
-            if (l.type != HY_LATENT_ATTENTION || !hy_mla_mma_supported(HyLatentAttn{l.heads, l.dim, l.rot_dim, l.vdim, l.kv_rank, l.rot_dims, l.scale})) continue;
-            bool have = false; for (const TileList& tl : tile_lists) have |= tl.heads == l.heads;
-            if (have) continue;
-            tile_seq_.clear(); tile_q0_.clear(); tile_k0_.clear(); tile_k1_.clear(); tile_slot_.clear(); merge_row_.clear(); merge_slot_.clear(); merge_parts_.clear();
-            int next_slot = 0;
-            for (int sq = 0; sq < S; ++sq) {
-                const int len = in.seq_row0[sq + 1] - in.seq_row0[sq], nq = len * l.heads, ctx = seq_pos0_[sq] + 1;
-                // a decoding row with a long context: its cache rows in 2..16 parts of >= 256 rows, one CTA each, joined afterwards.  The cut
-                // depends on the row's position only.
-                int parts = (len == 1 && nq <= HY_MLA_TILE_QUERIES) ? std::min(16, ctx / 256) : 1;
-                if (parts > 1 && next_slot + parts > split_slots_) parts = 1;
-                if (parts > 1) {
-                    const int per = ((ctx + parts - 1) / parts + 31) / 32 * 32; parts = (ctx + per - 1) / per;
-                    merge_row_.push_back(in.seq_row0[sq]); merge_slot_.push_back(next_slot); merge_parts_.push_back(parts);
-                    for (int pz = 0; pz < parts; ++pz) {
-                        tile_seq_.push_back(sq); tile_q0_.push_back(0); tile_k0_.push_back(pz * per); tile_k1_.push_back(std::min(ctx, (pz + 1) * per)); tile_slot_.push_back(next_slot++);
-                    }
-                    continue;
-                }
-                for (int q0 = 0; q0 < nq; q0 += HY_MLA_TILE_QUERIES) { tile_seq_.push_back(sq); tile_q0_.push_back(q0); tile_k0_.push_back(0); tile_k1_.push_back(0); tile_slot_.push_back(-1); }
+    // attention plans, one per attention layer.  Sequences that bring at least hy_unabsorbed_rows rows take the prefill form (keys / values of
+    // their context up-projected by a GEMM, ordinary multi-head attention); the others — decoding rows, short portions — the absorbed form:
+    // tiles of 64 consecutive (row, head) pairs of one sequence, a decoding row with a long context cut into parts.
+    struct TileList { bool mma = false, any_small = false; size_t o_seq = 0, o_q0 = 0, o_k0 = 0, o_k1 = 0, o_slot = 0, o_mrow = 0, o_mslot = 0, o_mparts = 0; int n = 0, n_merge = 0;
+                      size_t o_pseq = 0, o_phead = 0, o_prow0 = 0, o_base = 0; int n_ptiles = 0, ctx_rows = 0, max_ctx = 0; };
+    std::vector<TileList> tile_lists(hc_.layers.size());
+    for (size_t li = 0; li < hc_.layers.size(); ++li) {
+        const HyLayer& l = hc_.layers[li]; TileList& tl = tile_lists[li];
+        if (l.type != HY_LATENT_ATTENTION) continue;
+        const bool prefill_form = lw_[li].kv_up.tc && kv_ctx_;
+        tl.mma = !f32_ && opt.hy_tensor_core && hy_mla_mma_supported(HyLatentAttn{l.heads, l.dim, l.rot_dim, l.vdim, l.kv_rank, l.rot_dims, l.scale});
+        tile_seq_.clear(); tile_q0_.clear(); tile_k0_.clear(); tile_k1_.clear(); tile_slot_.clear(); merge_row_.clear(); merge_slot_.clear(); merge_parts_.clear();
+        ptile_seq_.clear(); ptile_head_.clear(); ptile_row0_.clear(); seq_base_.assign(S, -1);
+        int next_slot = 0;
+        for (int sq = 0; sq < S; ++sq) {
+            const int len = in.seq_row0[sq + 1] - in.seq_row0[sq], nq = len * l.heads, ctx_end = seq_pos0_[sq] + len;
+            // many rows, or a short portion that is a good part of its own context (the start of a prompt cut by the step's token budget)
+            if (prefill_form && (len >= opt.hy_unabsorbed_rows || (len >= 2 && ctx_end <= 8 * len)) && tl.ctx_rows + ctx_end <= ctx_cap_) {
+                seq_base_[sq] = tl.ctx_rows; tl.ctx_rows += ctx_end; tl.max_ctx = std::max(tl.max_ctx, ctx_end);
+                for (int hd = 0; hd < l.heads; ++hd) for (int q0 = 0; q0 < len; q0 += 64) { ptile_seq_.push_back(sq); ptile_head_.push_back(hd); ptile_row0_.push_back(q0); }
+                continue;
             }
-            TileList tl; tl.heads = l.heads; tl.n = (int)tile_seq_.size(); tl.n_merge = (int)merge_row_.size();
-            tl.o_seq = put(tile_seq_.data(), tile_seq_.size()); tl.o_q0 = put(tile_q0_.data(), tile_q0_.size());
-            tl.o_k0 = put(tile_k0_.data(), tile_k0_.size()); tl.o_k1 = put(tile_k1_.data(), tile_k1_.size()); tl.o_slot = put(tile_slot_.data(), tile_slot_.size());
-            tl.o_mrow = put(merge_row_.data(), merge_row_.size()); tl.o_mslot = put(merge_slot_.data(), merge_slot_.size()); tl.o_mparts = put(merge_parts_.data(), merge_parts_.size());
-            tile_lists.push_back(tl);
+            tl.any_small = true;
+            if (!tl.mma) continue;
+            const int ctx = seq_pos0_[sq] + 1;
+            // a decoding row with a long context: its cache rows in 2..16 parts of >= 256 rows, one CTA each, joined afterwards.  The cut
+            // depends on the row's position only.
+            int parts = (len == 1 && nq <= HY_MLA_TILE_QUERIES) ? std::min(16, ctx / 256) : 1;
+            if (parts > 1 && next_slot + parts > split_slots_) parts = 1;
+            if (parts > 1) {
+                const int per = ((ctx + parts - 1) / parts + 31) / 32 * 32; parts = (ctx + per - 1) / per;
+                merge_row_.push_back(in.seq_row0[sq]); merge_slot_.push_back(next_slot); merge_parts_.push_back(parts);
+                for (int pz = 0; pz < parts; ++pz) {
+                    tile_seq_.push_back(sq); tile_q0_.push_back(0); tile_k0_.push_back(pz * per); tile_k1_.push_back(std::min(ctx, (pz + 1) * per)); tile_slot_.push_back(next_slot++);
+                }
+                continue;
+            }
+            for (int q0 = 0; q0 < nq; q0 += HY_MLA_TILE_QUERIES) { tile_seq_.push_back(sq); tile_q0_.push_back(q0); tile_k0_.push_back(0); tile_k1_.push_back(0); tile_slot_.push_back(-1); }
         }
+        tl.n = (int)tile_seq_.size(); tl.n_merge = (int)merge_row_.size(); tl.n_ptiles = (int)ptile_seq_.size();
+        tl.o_seq = put(tile_seq_.data(), tile_seq_.size()); tl.o_q0 = put(tile_q0_.data(), tile_q0_.size());
+        tl.o_k0 = put(tile_k0_.data(), tile_k0_.size()); tl.o_k1 = put(tile_k1_.data(), tile_k1_.size()); tl.o_slot = put(tile_slot_.data(), tile_slot_.size());
+        tl.o_mrow = put(merge_row_.data(), merge_row_.size()); tl.o_mslot = put(merge_slot_.data(), merge_slot_.size()); tl.o_mparts = put(merge_parts_.data(), merge_parts_.size());
+        tl.o_pseq = put(ptile_seq_.data(), ptile_seq_.size()); tl.o_phead = put(ptile_head_.data(), ptile_head_.size()); tl.o_prow0 = put(ptile_row0_.data(), ptile_row0_.size());
+        tl.o_base = put(seq_base_.data(), seq_base_.size());
+    }
     cuda_check(cudaMemcpyAsync(d_meta_, hm, wd * 4, cudaMemcpyHostToDevice, stream), "meta H2D");
     cuda_check(cudaEventRecord(meta_ev_[meta_idx_], stream), "meta event");
     h2d_bytes += wd * 4;
@@ -462,27 +485,34 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
         if (l.type == HY_LATENT_ATTENTION) {
             const HyLatentAttn a{l.heads, l.dim, l.rot_dim, l.vdim, l.kv_rank, l.rot_dims, l.scale};
             const int E = l.kv_rank + l.rot_dim;
-            // absorbed queries: q_abs[t, h, :rank] = W_uk[h]^T q_unrotated[t, h]
-            const bool head_tc = !w.uk_heads.empty() && T >= 256;      // prefill-sized steps: one tcgen05 GEMM per head; smaller ones: one batched launch
-            if (head_tc) for (int hd = 0; hd < l.heads; ++hd) gemm(HY_STORE_F32, at(proj_, w.off_a + (size_t)hd * (l.dim + l.rot_dim)), ld_proj_, w.uk_heads[hd], q_abs_ + (size_t)hd * E, l.heads * E, T, nullptr, 1.f);
-            else cuda_check(hy_gemm(f32_, HY_STORE_F32, at(proj_, w.off_a), ld_proj_, w.uk_t, l.dim, q_abs_, l.heads * E, T, l.kv_rank, l.dim, nullptr, 1.f, l.heads,
-                                    l.dim + l.rot_dim, (long long)l.kv_rank * l.dim, E, stream), "query absorption");
-            MARK(3);
+            const TileList& tl = tile_lists[run.layer];
             cuda_check(hy_mla_prep(f32_, a, at(proj_, w.off_a), ld_proj_, at(proj_, w.off_b), ld_proj_, w.dkv_norm, hc_.eps, ropes_[w.rope].cos, ropes_[w.rope].sin,
                                    caches_[run.cache_idx], q_abs_, r, stream), "latent cache write"); MARK(4);
-            const TileList* tl = nullptr; for (const TileList& t : tile_lists) if (t.heads == l.heads && hy_mla_mma_supported(a)) tl = &t;
-            if (tl) {
-                HyMlaSplit sp{nullptr, nullptr, nullptr, split_o_, split_ml_};
-                if (tl->n_merge > 0) { sp.tile_k0 = d_meta_ + tl->o_k0; sp.tile_k1 = d_meta_ + tl->o_k1; sp.tile_slot = d_meta_ + tl->o_slot; }
-                cuda_check(hy_mla_attention_mma(a, q_abs_, caches_[run.cache_idx], lat_, r, d_meta_ + tl->o_seq, d_meta_ + tl->o_q0, tl->n, sp, stream), "latent attention (mma)");
-                cuda_check(hy_mla_merge(d_meta_ + tl->o_mrow, d_meta_ + tl->o_mslot, d_meta_ + tl->o_mparts, tl->n_merge, split_o_, split_ml_, lat_, l.heads, l.kv_rank, stream), "latent attention (join)");
+            if (tl.any_small) {
+                // absorbed queries: q_abs[t, h, :rank] = W_uk[h]^T q_unrotated[t, h]
+                const bool head_tc = !w.uk_heads.empty() && T >= 256;      // prefill-sized steps: one tcgen05 GEMM per head; smaller ones: one batched launch
+                if (head_tc) for (int hd = 0; hd < l.heads; ++hd) gemm(HY_STORE_F32, at(proj_, w.off_a + (size_t)hd * (l.dim + l.rot_dim)), ld_proj_, w.uk_heads[hd], q_abs_ + (size_t)hd * E, l.heads * E, T, nullptr, 1.f);
+                else cuda_check(hy_gemm(f32_, HY_STORE_F32, at(proj_, w.off_a), ld_proj_, w.uk_t, l.dim, q_abs_, l.heads * E, T, l.kv_rank, l.dim, nullptr, 1.f, l.heads,
+                                        l.dim + l.rot_dim, (long long)l.kv_rank * l.dim, E, stream), "query absorption");
+                MARK(3);
+                if (tl.mma) {
+                    HyMlaSplit sp{nullptr, nullptr, nullptr, split_o_, split_ml_};
+                    if (tl.n_merge > 0) { sp.tile_k0 = d_meta_ + tl.o_k0; sp.tile_k1 = d_meta_ + tl.o_k1; sp.tile_slot = d_meta_ + tl.o_slot; }
+                    cuda_check(hy_mla_attention_mma(a, q_abs_, caches_[run.cache_idx], lat_, r, d_meta_ + tl.o_seq, d_meta_ + tl.o_q0, tl.n, sp, stream), "latent attention (mma)");
+                    cuda_check(hy_mla_merge(d_meta_ + tl.o_mrow, d_meta_ + tl.o_mslot, d_meta_ + tl.o_mparts, tl.n_merge, split_o_, split_ml_, lat_, l.heads, l.kv_rank, stream), "latent attention (join)");
+                } else cuda_check(hy_mla_attention(f32_, a, q_abs_, caches_[run.cache_idx], lat_, r, stream), "latent attention");
+                MARK(5);
+                if (head_tc) for (int hd = 0; hd < l.heads; ++hd) gemm(HY_STORE, at(lat_, (size_t)hd * l.kv_rank), l.heads * l.kv_rank, w.uv_heads[hd], at(mix_, (size_t)hd * l.vdim), ld_mix_, T, nullptr, 1.f);
+                else cuda_check(hy_gemm(f32_, HY_STORE, lat_, l.heads * l.kv_rank, w.uv, l.kv_rank, mix_, ld_mix_, T, l.vdim, l.kv_rank, nullptr, 1.f, l.heads, l.kv_rank,
+                                        (long long)l.vdim * l.kv_rank, l.vdim, stream), "value up-projection");
+                MARK(3);
             }
-            else cuda_check(hy_mla_attention(f32_, a, q_abs_, caches_[run.cache_idx], lat_, r, stream), "latent attention");
-            MARK(5);
-            if (head_tc) for (int hd = 0; hd < l.heads; ++hd) gemm(HY_STORE, at(lat_, (size_t)hd * l.kv_rank), l.heads * l.kv_rank, w.uv_heads[hd], at(mix_, (size_t)hd * l.vdim), ld_mix_, T, nullptr, 1.f);
-            else cuda_check(hy_gemm(f32_, HY_STORE, lat_, l.heads * l.kv_rank, w.uv, l.kv_rank, mix_, ld_mix_, T, l.vdim, l.kv_rank, nullptr, 1.f, l.heads, l.kv_rank,
-                                    (long long)l.vdim * l.kv_rank, l.vdim, stream), "value up-projection");
-            MARK(3);
+            if (tl.n_ptiles > 0) {      // prefill form for the sequences that bring many rows (after the absorbed path, whose up-projection wrote every row of mix_)
+                cuda_check(hy_gather_ctx(caches_[run.cache_idx], E, r, d_meta_ + tl.o_base, tl.max_ctx, lat_ctx_, stream), "context gather");
+                gemm(HY_STORE, lat_ctx_, E, w.kv_up, kv_ctx_, ld_kv_, tl.ctx_rows, nullptr, 1.f); MARK(20);
+                cuda_check(hy_mha_prefill(a, at(proj_, w.off_a), ld_proj_, q_abs_, kv_ctx_, ld_kv_, lat_ctx_, mix_, ld_mix_, r, d_meta_ + tl.o_pseq, d_meta_ + tl.o_phead,
+                                          d_meta_ + tl.o_prow0, d_meta_ + tl.o_base, tl.n_ptiles, stream), "attention (prefill form)"); MARK(21);
+            }
         } else if (l.type == HY_CHANNEL_DELTA) {
             const HyDelta d{l.heads, l.kv_heads, l.dim, l.vdim};
             cuda_check(hy_conv_silu(f32_, at(proj_, w.off_a), ld_proj_, w.conv_ch, w.conv_w, nullptr, l.conv, conv_, ld_conv_, tails_[run.state_idx], r, stream), "conv");

@@ -30,7 +30,7 @@ private:
     struct HostMat { int N = 0, K = 0; std::vector<float> v; };
     struct LayerW {
         float* norm1 = nullptr;
-        Mat in, a2, g2, o, router;
+        Mat in, a2, g2, o, router, kv_up;
         int off_a = 0, off_b = 0, off_c = 0, off_d = 0;   // column offsets of the fused input projection's segments (see hybrid_model.cpp)
         int a_rank = 0, g_rank = 0;
         void *uk_t = nullptr, *uv = nullptr; float* dkv_norm = nullptr; int rope = -1;      // latent attention
@@ -68,6 +68,8 @@ private:
     int32_t* h_meta_buf_[2] = {nullptr, nullptr}; cudaEvent_t meta_ev_[2] = {nullptr, nullptr}; int meta_idx_ = 0;
     int32_t* d_meta_ = nullptr; size_t meta_cap_words_ = 0;
     std::vector<int32_t> row_seq_, seq_pos0_, tile_seq_, tile_q0_, tile_k0_, tile_k1_, tile_slot_, merge_row_, merge_slot_, merge_parts_;
+    std::vector<int32_t> ptile_seq_, ptile_head_, ptile_row0_, seq_base_;
+    void *lat_ctx_ = nullptr, *kv_ctx_ = nullptr; int ld_kv_ = 0, ctx_cap_ = 0;    // prefill form of attention: gathered cache rows of whole contexts and their keys / values
     float *split_o_ = nullptr, *split_ml_ = nullptr; int split_slots_ = 0;       // partials of decoding rows whose cache rows are cut into parts
 };
 
