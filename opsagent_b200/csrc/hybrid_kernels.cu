@@ -547,6 +547,59 @@ __global__ void hy_conv_silu_kernel(const TA* in, int ld_in, int C, const float*
     for (int j = 0; j < taps; ++j) acc = fmaf(w[c * taps + j], conv_input(in, ld_in, C, tail, taps, row0, pos0, i - (taps - 1) + j, c), acc);
     stf(out + (long long)t * ld_out + c, siluf_(acc));
 }
+// bf16 rows of prefill-sized steps whose channels come in aligned groups of 8: a thread computes 8 channels of CONV_ROWS consecutive rows
+// from 16-byte loads, with its taps' weights and the last inputs in registers, so that every input row is read once.  The sum runs over
+// the taps in the same order as in the kernel above: both give the same bits.
+constexpr int CONV_ROWS = 16;
+__device__ __forceinline__ void bf8_to_f32(const uint4& u, float* f) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+template <int TAPS>
+__global__ void __launch_bounds__(128) hy_conv_silu_vec8_kernel(const __nv_bfloat16* __restrict__ in, int ld_in, int C, const float* __restrict__ w, const float* __restrict__ bias,
+                                                                 __nv_bfloat16* __restrict__ out, int ld_out, const __nv_bfloat16* __restrict__ tails, HyRows r) {
+    HY_PDL();
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8, t0 = blockIdx.y * CONV_ROWS;
+    if (c >= C) return;
+    float wr[TAPS][8], win[TAPS][8], b8[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        b8[e] = bias ? bias[c + e] : 0.f;
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) wr[j][e] = w[(c + e) * TAPS + j];
+    }
+    for (int tt = 0; tt < CONV_ROWS && t0 + tt < r.T; ++tt) {
+        const int t = t0 + tt, seq = r.row_seq[t], row0 = r.seq_row0[seq], i = t - row0;
+        if (tt == 0 || i == 0) {                        // the inputs before this row: earlier rows of the step, the carried tail, or zeros
+            const int pos0 = r.seq_pos0[seq];
+            const __nv_bfloat16* tail = tails + (long long)r.seq_state[seq] * (TAPS - 1) * C;
+#pragma unroll
+            for (int j = 0; j < TAPS - 1; ++j) {
+                const int src = i - (TAPS - 1) + j;
+                uint4 u = make_uint4(0u, 0u, 0u, 0u);
+                if (src >= 0) u = *reinterpret_cast<const uint4*>(in + (long long)(row0 + src) * ld_in + c);
+                else if (pos0 > 0) u = *reinterpret_cast<const uint4*>(tail + (long long)(TAPS - 1 + src) * C + c);
+                bf8_to_f32(u, win[j]);
+            }
+        }
+        bf8_to_f32(*reinterpret_cast<const uint4*>(in + (long long)t * ld_in + c), win[TAPS - 1]);
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float a0 = b8[2 * e], a1 = b8[2 * e + 1];
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j) { a0 = fmaf(wr[j][2 * e], win[j][2 * e], a0); a1 = fmaf(wr[j][2 * e + 1], win[j][2 * e + 1], a1); }
+            const __nv_bfloat162 h = __floats2bfloat162_rn(siluf_(a0), siluf_(a1));
+            o[e] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(out + (long long)t * ld_out + c) = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+        for (int j = 0; j < TAPS - 1; ++j)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) win[j][e] = win[j + 1][e];
+    }
+}
 template <typename TA>
 __global__ void hy_conv_tails_kernel(const TA* in, int ld_in, int C, int taps, TA* tails, HyRows r) {
     HY_PDL();
@@ -753,6 +806,58 @@ __global__ void __launch_bounds__(128) hy_gated_norm_kernel(const float* o, int 
         v = v * rr * w[c % wlen];
         if (!gate_before) v *= ga;
         stf(out + (long long)t * ld_out + c, v);
+    }
+}
+
+// The same for groups that one warp handles well (prefill-sized steps): a warp per (row, group), four consecutive channels per lane and
+// step, no block barrier.  The second pass re-reads what the first left in L1.
+__device__ __forceinline__ void ld4(const float* p, float* f) { const float4 u = *reinterpret_cast<const float4*>(p); f[0] = u.x; f[1] = u.y; f[2] = u.z; f[3] = u.w; }
+__device__ __forceinline__ void ld4(const __nv_bfloat16* p, float* f) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xffff0000u); f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xffff0000u);
+}
+__device__ __forceinline__ void st4(float* p, const float* f) { *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]); }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, const float* f) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+template <typename TA>
+__global__ void __launch_bounds__(128) hy_gated_norm_warp_kernel(const float* __restrict__ o, int C, int group, const float* __restrict__ w, int wlen, const TA* __restrict__ gate,
+                                                                  int ld_gate, int gate_before, int act, const float* __restrict__ skip, int skip_block, const TA* __restrict__ xs,
+                                                                  int ld_xs, TA* __restrict__ out, int ld_out, float eps, long long n_items) {
+    HY_PDL();
+    const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (item >= n_items) return;
+    const int lane = threadIdx.x & 31, G = C / group, t = (int)(item / G), c0 = (int)(item % G) * group;
+    float ss = 0.f, v[4], g[4], x4[4];
+    for (int i = lane * 4; i < group; i += 128) {
+        const int c = c0 + i;
+        ld4(o + (long long)t * C + c, v);
+        if (skip) { ld4(xs + (long long)t * ld_xs + c, x4);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = fmaf(skip[(c + e) / skip_block], x4[e], v[e]); }
+        if (gate_before) { ld4(gate + (long long)t * ld_gate + c, g);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] *= act ? siluf_(g[e]) : sigmoidf_(g[e]); }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ss += v[e] * v[e];
+    }
+    const float rr = 1.0f / sqrtf(warp_sum(ss) / (float)group + eps);
+    for (int i = lane * 4; i < group; i += 128) {
+        const int c = c0 + i;
+        ld4(o + (long long)t * C + c, v);
+        if (skip) { ld4(xs + (long long)t * ld_xs + c, x4);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = fmaf(skip[(c + e) / skip_block], x4[e], v[e]); }
+        ld4(gate + (long long)t * ld_gate + c, g);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float ga = act ? siluf_(g[e]) : sigmoidf_(g[e]);
+            if (gate_before) v[e] *= ga;
+            v[e] = v[e] * rr * w[(c + e) % wlen];
+            if (!gate_before) v[e] *= ga;
+        }
+        st4(out + (long long)t * ld_out + c, v);
     }
 }
 
@@ -1072,6 +1177,15 @@ cudaError_t hy_mha_prefill(const HyLatentAttn& a, const void* q, int ldq, const 
 }
 cudaError_t hy_conv_silu(bool f32, const void* in, int ld_in, int C, const float* w, const float* bias, int taps, void* out, int ld_out, const void* tails, const HyRows& r,
                          cudaStream_t s) {
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (!f32 && r.T >= 512 && taps >= 2 && taps <= 4 && C % 8 == 0 && ld_in % 8 == 0 && ld_out % 8 == 0 && al16(in) && al16(out) && al16(tails)) {
+        const dim3 g((C / 8 + 127) / 128, (r.T + CONV_ROWS - 1) / CONV_ROWS);
+        switch (taps) {
+            case 2: return launch_plain(hy_conv_silu_vec8_kernel<2>, g, dim3(128), 0, s, (const bf*)in, ld_in, C, w, bias, (bf*)out, ld_out, (const bf*)tails, r);
+            case 3: return launch_plain(hy_conv_silu_vec8_kernel<3>, g, dim3(128), 0, s, (const bf*)in, ld_in, C, w, bias, (bf*)out, ld_out, (const bf*)tails, r);
+            default: return launch_plain(hy_conv_silu_vec8_kernel<4>, g, dim3(128), 0, s, (const bf*)in, ld_in, C, w, bias, (bf*)out, ld_out, (const bf*)tails, r);
+        }
+    }
     dim3 grid((C + 127) / 128, r.T);
     return f32 ? launch_plain(hy_conv_silu_kernel<float>, grid, dim3(128), 0, s, (const float*)in, ld_in, C, w, bias, taps, (float*)out, ld_out, (const float*)tails, r)
                : launch_plain(hy_conv_silu_kernel<bf>, grid, dim3(128), 0, s, (const bf*)in, ld_in, C, w, bias, taps, (bf*)out, ld_out, (const bf*)tails, r);
@@ -1121,6 +1235,15 @@ cudaError_t hy_recurrence(bool delta, const float* qq, const float* kk, const fl
 }
 cudaError_t hy_gated_norm(bool f32, const float* o, int C, int group, const float* w, int wlen, const void* gate, int ld_gate, int gate_before, int act, const float* skip,
                           int skip_block, const void* xs, int ld_xs, void* out, int ld_out, float eps, int T, cudaStream_t s) {
+    // The choice of kernel rests on the sizes of the model only, never on the step: a row's bits do not depend on its batch.
+    const size_t ea = f32 ? 4 : 2;
+    auto al = [](const void* p, size_t a) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; };
+    if (group % 4 == 0 && group <= 512 && C % 4 == 0 && ld_gate % 4 == 0 && ld_out % 4 == 0 && (!skip || ld_xs % 4 == 0) && al(o, 16) && al(gate, 4 * ea) && al(out, 4 * ea) && al(xs, 4 * ea)) {
+        const long long n = (long long)T * (C / group);
+        const dim3 g((unsigned)((n + 3) / 4));
+        return f32 ? launch_plain(hy_gated_norm_warp_kernel<float>, g, dim3(128), 0, s, o, C, group, w, wlen, (const float*)gate, ld_gate, gate_before, act, skip, skip_block, (const float*)xs, ld_xs, (float*)out, ld_out, eps, n)
+                   : launch_plain(hy_gated_norm_warp_kernel<bf>, g, dim3(128), 0, s, o, C, group, w, wlen, (const bf*)gate, ld_gate, gate_before, act, skip, skip_block, (const bf*)xs, ld_xs, (bf*)out, ld_out, eps, n);
+    }
     dim3 grid(T, C / group);
     return f32 ? launch_plain(hy_gated_norm_kernel<float>, grid, dim3(128), 0, s, o, C, group, w, wlen, (const float*)gate, ld_gate, gate_before, act, skip, skip_block, (const float*)xs, ld_xs, (float*)out, ld_out, eps)
                : launch_plain(hy_gated_norm_kernel<bf>, grid, dim3(128), 0, s, o, C, group, w, wlen, (const bf*)gate, ld_gate, gate_before, act, skip, skip_block, (const bf*)xs, ld_xs, (bf*)out, ld_out, eps);

@@ -215,6 +215,30 @@ def test_tensor_core_attention_sizes(tmp_path):
         assert O.rel_err(got.astype(np.float64), outs[1][0].astype(np.float64)).max() < 3 * SAME_TOL      # in another order, and these scores are sharp)
 
 
+def test_prefill_sized_steps_of_the_recurrent_layers(tmp_path):
+    """Steps of 512 rows and more take the convolution kernel that walks 16 rows per thread, smaller steps the one-row kernel: a prompt
+    whole, the same prompt in portions below that size, and two requests sharing a large step (one continuing from its carried tail, the
+    other starting in the middle of a 16-row block) agree with each other and with the oracle.  No routed experts: nothing can flip."""
+    layers = [O.delta_layer(heads=4, kv_heads=2, dim=16, vdim=32, conv=4), O.mamba_layer(heads=4, vdim=16, state=16, groups=2, norm_groups=2, conv=3),
+              O.delta_layer(heads=2, kv_heads=2, dim=32, vdim=64, conv=2), O.mamba_layer(heads=2, vdim=64, state=24, groups=1, norm_groups=1, conv=4)]
+    cfg = O.make_config(layers, width=64, vocab=70)
+    W = checkpoint(tmp_path, cfg, seed=17)
+    A, B = tokens_of(cfg, 620, 14), tokens_of(cfg, 270, 15)
+    want_a, want_b = O.forward(cfg, W, A), O.forward(cfg, W, B)
+    with engine(tmp_path, "bfloat16", pages=16, slots=2) as eng:
+        whole_a, whole_b = replay(eng, 1, A, [620]), replay(eng, 2, B, [270])
+        cut_a = replay(eng, 3, A, [100, 100, 100, 100, 100, 100, 18])
+        parts = [eng.trace_step([(4, A[:40], list(range(40)))], []),
+                 eng.trace_step([(4, A[40:340], list(range(300))), (5, B[:250], list(range(250)))], []),
+                 eng.trace_step([(4, A[340:], list(range(280))), (5, B[250:], list(range(20)))], [4, 5])]
+        mixed_a = np.concatenate([parts[0], parts[1][:300], parts[2][:280]])
+        mixed_b = np.concatenate([parts[1][300:], parts[2][280:]])
+    for got, ref in ((cut_a, whole_a), (mixed_a, whole_a), (mixed_b, whole_b)):
+        assert O.rel_err(got.astype(np.float64), ref.astype(np.float64)).max() < SAME_TOL
+    for got, want in ((whole_a, want_a), (whole_b, want_b), (mixed_a, want_a), (mixed_b, want_b)):
+        assert O.rel_err(got.astype(np.float64), want).max() < BF16_TOL
+
+
 def test_greedy_generation_through_the_scheduler(tmp_path):
     """oa_tokens_submit -> continuous batching -> greedy sampling: three requests on two state slots (one waits for a slot), each compared
     with the oracle's greedy continuation wherever the oracle's top-1 margin is not a near tie."""
