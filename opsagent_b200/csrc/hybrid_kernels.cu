@@ -1140,7 +1140,9 @@ cudaError_t hy_mla_attention_mma(const HyLatentAttn& a, const float* q_abs, cons
     if (!nvb) return cudaErrorInvalidValue;
     // 32-row tiles when two CTAs (8 warps) still fit an SM's shared memory or nothing smaller would make them fit; else 16-row tiles
     // (a step with few tiles — decoding — is a latency chain per CTA: the larger tile halves its length)
-    const bool kt32 = mla_mma_smem(E, 32) <= 113 * 1024 || mla_mma_smem(E, 16) > 113 * 1024 || n_tiles * (a.kv_rank / (nvb * 8)) < 296;
+    // — and never a tile that the 200 KB opt-in limit does not hold (wide latents: only the 16-row tile is left)
+    const bool kt32 = mla_mma_smem(E, 32) <= 200 * 1024 &&
+                      (mla_mma_smem(E, 32) <= 113 * 1024 || mla_mma_smem(E, 16) > 113 * 1024 || n_tiles * (a.kv_rank / (nvb * 8)) < 296);
 #define HY_MLA(NVB) (kt32 ? mla_mma_launch<NVB, 32>(a, q_abs, cache, lat_out, r, tile_seq, tile_q0, n_tiles, sp, s) : mla_mma_launch<NVB, 16>(a, q_abs, cache, lat_out, r, tile_seq, tile_q0, n_tiles, sp, s))
     return nvb == 32 ? HY_MLA(32) : nvb == 16 ? HY_MLA(16) : HY_MLA(8);
 #undef HY_MLA

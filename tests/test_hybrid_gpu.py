@@ -215,6 +215,42 @@ def test_tensor_core_attention_sizes(tmp_path):
         assert O.rel_err(got.astype(np.float64), outs[1][0].astype(np.float64)).max() < 3 * SAME_TOL      # in another order, and these scores are sharp)
 
 
+def test_wide_latent_takes_the_small_cache_tile(tmp_path):
+    """A latent row so wide that only the 16-row cache tile of the tensor-core kernel fits shared memory (the 32-row tile does not): decoding
+    rows and short portions behind a long context (absorbed form) and whole prompts (prefill form) against the oracle."""
+    cfg = O.make_config([O.attention_layer(heads=2, dim=16, rot_dim=32, vdim=16, kv_rank=768)], width=64, vocab=96)
+    W = checkpoint(tmp_path, cfg, seed=19)
+    toks = tokens_of(cfg, 180, 12)
+    want = O.forward(cfg, W, toks)
+    with engine(tmp_path, "bfloat16", pages=4) as eng:
+        for cuts in ([180], [150, 5, 3, 2], [40]):
+            e = O.rel_err(replay(eng, 1, toks, cuts).astype(np.float64), want)
+            assert np.quantile(e, 0.95) < 0.06 and e.max() < 0.2, f"cuts {cuts}: 95% {np.quantile(e, 0.95):.3e}, worst {e.max():.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_router_with_negative_choice_scores(tmp_path, dtype):
+    """Corrections far below zero make every choice score negative, so an expert of a dropped group must count as minus infinity (a zero
+    would beat every kept expert); corrections that differ by more than the scores' range make the correction, not the score, pick the
+    experts, while the weights still come from the uncorrected scores.  The oracle shows that both matter before the engine is asked."""
+    mlp = O.moe(experts=8, top=3, groups=4, keep=2, ff=16, scale=1.7)
+    cfg = O.make_config([O.mamba_layer(mlp=mlp), O.attention_layer(mlp=mlp)], width=40, vocab=60)
+    W = O.random_weights(cfg, 23)
+    rng = np.random.default_rng(5)
+    for i in range(2):
+        W["l%d.mlp.correction" % i] = O.bf16_round(-3.0 + 1.5 * rng.standard_normal(8)).astype(np.float64)
+    O.write_checkpoint(str(tmp_path), cfg, W)
+    toks = tokens_of(cfg, 70, 3)
+    want = O.forward(cfg, W, toks)
+    plain = dict(W)
+    for i in range(2):
+        plain["l%d.mlp.correction" % i] = np.zeros(8)
+    assert O.rel_err(O.forward(cfg, plain, toks), want).max() > 0.05          # the corrections change the answer
+    with engine(tmp_path, dtype) as eng:
+        check(replay(eng, 1, toks, [70]), want, dtype)
+        check(replay(eng, 2, toks, [33, 2, 30]), want, dtype)
+
+
 def test_prefill_sized_steps_of_the_recurrent_layers(tmp_path):
     """Steps of 512 rows and more take the convolution kernel that walks 16 rows per thread, smaller steps the one-row kernel: a prompt
     whole, the same prompt in portions below that size, and two requests sharing a large step (one continuing from its carried tail, the
