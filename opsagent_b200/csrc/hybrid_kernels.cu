@@ -691,8 +691,10 @@ __global__ void __launch_bounds__(REC_COLS) hy_recurrence_kernel(const float* qq
 }
 
 // Register-resident variant for dim <= DM (dim and vdim multiples of 4): a state column (value channel) lives in the registers of LANES
-// adjacent lanes (LANES = 1: one thread holds all DM rows and a step needs no cross-lane traffic; LANES = 4: four lanes hold a quarter each
-// and the two dot products of a step meet through two shuffles — four times the threads for steps with few sequences).  The per-token operands (q, k, decay rows, 128 values, the scalar)
+// threads (LANES = 1: one thread holds all DM rows, 128 columns per CTA, and a step needs no traffic between threads; LANES = 4: the CTA's
+// four warps hold a quarter of the rows each for the same 32 columns — a lane is a column, so the operand reads stay warp-wide broadcasts —
+// and a token's per-token chain is a quarter as long: the delta rule's dot product meets through shared memory and one more barrier per
+// token, the read-out's four partial sums are joined one token later by one of the warps, off the chain).  The per-token operands (q, k, decay rows, 128 values, the scalar)
 // arrive through an 8-deep cp.async ring in shared memory — every thread keeps its own source pointer and advances it by a constant per
 // token — and are read from there as 16-byte broadcasts.  The dependent chains of a step are split over four accumulators.  128 / LANES
 // columns per CTA.  The order of every sum is fixed for a given LANES, and LANES is chosen from the sizes alone, never from the step.
@@ -705,7 +707,8 @@ __global__ void __launch_bounds__(128) hy_recurrence_reg_kernel(const float* __r
     extern __shared__ __align__(16) float rec_ring[];
     constexpr int stride = 3 * DM + REC_CTA_COLS + 4;     // floats per stage: q[DM] k[DM] g[DM] v[128] scalar (padded to 16 bytes); pad rows: q = k = 0, decay 1
     constexpr int DR = DM / LANES, COLS = REC_CTA_COLS / LANES;       // rows per thread, columns per CTA
-    const int tid = threadIdx.x, part = tid % LANES, cl = tid / LANES, col = blockIdx.z * COLS + cl, r0 = part * DR;
+    const int tid = threadIdx.x, part = tid / COLS, cl = tid % COLS, col = blockIdx.z * COLS + cl, r0 = part * DR;      // LANES = 4: part = warp
+    __shared__ float rec_pd[LANES][COLS], rec_po[2][LANES][COLS];      // partial dot products of the current token; partial read-outs of this and the last token
     const int seq = blockIdx.x, h = blockIdx.y;
     const bool ok = col < VD;
     const int row0 = r.seq_row0[seq], len = r.seq_row0[seq + 1] - row0, pos0 = r.seq_pos0[seq], qh = h / (H / QH);
@@ -739,10 +742,14 @@ __global__ void __launch_bounds__(128) hy_recurrence_reg_kernel(const float* __r
     };
     for (int i = 0; i < REC_STAGES - 1; ++i) issue();
     float* op = out + ((long long)row0 * H + h) * VD + col;
+    auto join = [&](int i) {                         // LANES = 4: token i's read-out, its four partial sums added in warp order by warp i % 4
+        if (ok && part == (i & 3)) { const float* p = &rec_po[i & 1][0][cl]; op[(long long)i * H * VD] = (p[0] + p[COLS]) + (p[2 * COLS] + p[3 * COLS]); }
+    };
     for (int i = 0; i < len; ++i) {
         asm volatile("cp.async.wait_group %0;" ::"n"(REC_STAGES - 2) : "memory");
         __syncthreads();                             // token i has landed for everybody; slot (i - 1) % STAGES is free again
         issue();
+        if (LANES == 4 && i > 0) join(i - 1);        // its partials were written before this barrier; their buffer is written again at token i + 1, behind the next one
         const float* slot = rec_ring + (i % REC_STAGES) * stride;
         const float v = slot[3 * DM + cl], sc = slot[3 * DM + REC_CTA_COLS];
         const float* sq = slot + r0; const float* sk = slot + DM + r0; const float* sg = slot + 2 * DM + r0;
@@ -756,7 +763,11 @@ __global__ void __launch_bounds__(128) hy_recurrence_reg_kernel(const float* __r
                 d0 = fmaf(S[j], k4.x, d0); d1 = fmaf(S[j + 1], k4.y, d1); d2 = fmaf(S[j + 2], k4.z, d2); d3 = fmaf(S[j + 3], k4.w, d3);
             }
             float dot = (d0 + d1) + (d2 + d3);
-            if (LANES == 4) { dot += __shfl_xor_sync(0xffffffffu, dot, 1); dot += __shfl_xor_sync(0xffffffffu, dot, 2); }
+            if (LANES == 4) {                        // every thread reads the partials before it reaches the next token's first barrier, behind which they are written again
+                rec_pd[part][cl] = dot;
+                __syncthreads();
+                dot = (rec_pd[0][cl] + rec_pd[1][cl]) + (rec_pd[2][cl] + rec_pd[3][cl]);
+            }
             const float u = sc * (v - dot);
 #pragma unroll
             for (int j = 0; j < DR; j += 4) {
@@ -773,10 +784,10 @@ __global__ void __launch_bounds__(128) hy_recurrence_reg_kernel(const float* __r
             }
         }
         float o = (o0 + o1) + (o2 + o3);
-        if (LANES == 4) { o += __shfl_xor_sync(0xffffffffu, o, 1); o += __shfl_xor_sync(0xffffffffu, o, 2); }
-        if (ok && part == 0) *op = o;
-        op += (long long)H * VD;
+        if (LANES == 4) rec_po[i & 1][part][cl] = o;
+        else if (ok) op[(long long)i * H * VD] = o;
     }
+    if (LANES == 4 && len > 0) { __syncthreads(); join(len - 1); }
     if (ok)
 #pragma unroll
         for (int i = 0; i < DR; ++i) if (r0 + i < D) st[(long long)(r0 + i) * VD + col] = S[i];
@@ -1211,9 +1222,9 @@ cudaError_t hy_mamba_prep(bool f32, const HyMamba& m, const void* conv, int ld_c
 cudaError_t hy_recurrence(bool delta, const float* qq, const float* kk, const float* vv, const float* dec, const float* beta, float* out, float* state, int heads,
                           int qk_heads, int dim, int vdim, const HyRows& r, cudaStream_t s) {
     if (dim <= 128 && dim % 4 == 0 && vdim % 4 == 0) {
-        // measured (batch 16 x 1024 tokens, dim 128): four lanes per column 23.1 ms against 7.3 ms with one, although it has four times
-        // the warps — the broadcast reads of a warp become four-way, and the shuffles join the chain.  One lane per column everywhere.
-        const bool wide = false;
+        // one thread per column runs a chain of 4 dim dependent-ish operations per token with one or two warps per scheduler; beyond 32
+        // rows the rows are split over the CTA's four warps (by the sizes alone: the order of a sum never depends on the step)
+        const bool wide = dim > 32;
         dim3 grid(r.S, heads, (vdim * (wide ? 4 : 1) + REC_CTA_COLS - 1) / REC_CTA_COLS);
         const int dm = dim <= 32 ? 32 : dim <= 64 ? 64 : 128;
         const size_t ring = (size_t)REC_STAGES * (3 * dm + REC_CTA_COLS + 4) * 4;

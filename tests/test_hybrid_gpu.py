@@ -251,6 +251,27 @@ def test_router_with_negative_choice_scores(tmp_path, dtype):
         check(replay(eng, 2, toks, [33, 2, 30]), want, dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_recurrence_with_rows_split_over_warps(tmp_path, dtype):
+    """State sizes beyond 32 rows split a column's rows over a CTA's four warps: key sizes that fill the 64- and 128-row variants and one
+    that leaves padding rows, value sizes that are no multiple of the 32 columns of a CTA; whole, in portions, and token by token (a
+    one-token step joins its read-out after the loop), two sequences in one step."""
+    layers = [O.delta_layer(heads=2, kv_heads=1, dim=64, vdim=40, conv=3), O.mamba_layer(heads=2, vdim=24, state=128, groups=1, norm_groups=1, conv=2),
+              O.delta_layer(heads=3, kv_heads=3, dim=100, vdim=8, conv=2), O.mamba_layer(heads=4, vdim=36, state=48, groups=2, norm_groups=2, conv=4)]
+    cfg = O.make_config(layers, width=64, vocab=70)
+    W = checkpoint(tmp_path, cfg, seed=29)
+    A, B = tokens_of(cfg, 100, 16), tokens_of(cfg, 45, 17)
+    want_a, want_b = O.forward(cfg, W, A), O.forward(cfg, W, B)
+    with engine(tmp_path, dtype, pages=6, slots=2) as eng:
+        check(replay(eng, 1, A, [100]), want_a, dtype)
+        check(replay(eng, 2, A, [1, 2, 61, 3, 20]), want_a, dtype)
+        parts = [eng.trace_step([(3, A[:70], list(range(70))), (4, B[:5], list(range(5)))], []),
+                 eng.trace_step([(3, A[70:71], [0]), (4, B[5:], list(range(40)))], [4]),
+                 eng.trace_step([(3, A[71:], list(range(29)))], [3])]
+        check(np.concatenate([parts[0][:70], parts[1][:1], parts[2]]), want_a, dtype)
+        check(np.concatenate([parts[0][70:], parts[1][1:]]), want_b, dtype)
+
+
 def test_prefill_sized_steps_of_the_recurrent_layers(tmp_path):
     """Steps of 512 rows and more take the convolution kernel that walks 16 rows per thread, smaller steps the one-row kernel: a prompt
     whole, the same prompt in portions below that size, and two requests sharing a large step (one continuing from its carried tail, the
