@@ -161,6 +161,10 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tcgen05_kernel(const __grid
                                 f[0] += bf16lo(bb.x); f[1] += bf16hi(bb.x); f[2] += bf16lo(bb.y); f[3] += bf16hi(bb.y);
                                 f[4] += bf16lo(bb.z); f[5] += bf16hi(bb.z); f[6] += bf16lo(bb.w); f[7] += bf16hi(bb.w);
                             }
+                            if (p.store_act == 1) {
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) { const float r = fmaxf(f[i], 0.f); f[i] = r * r; }
+                            }
                             uint4 o;
                             o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
                             o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
@@ -488,6 +492,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_persistent_kernel(const 
                                     const uint4 bb = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col);
                                     f[0] += bf16lo(bb.x); f[1] += bf16hi(bb.x); f[2] += bf16lo(bb.y); f[3] += bf16hi(bb.y);
                                     f[4] += bf16lo(bb.z); f[5] += bf16hi(bb.z); f[6] += bf16lo(bb.w); f[7] += bf16hi(bb.w);
+                                }
+                                if (p.store_act == 1) {
+#pragma unroll
+                                    for (int k = 0; k < 8; ++k) { const float r = fmaxf(f[k], 0.f); f[k] = r * r; }
                                 }
                             } else {
                                 const uint4 rr = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.resid) + (size_t)row * p.ldr + col);

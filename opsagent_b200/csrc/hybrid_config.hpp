@@ -1,7 +1,10 @@
-// hybrid_config.hpp — configuration of the hybrid decoder family ("Ratasun"): a stack of parallel-residual layers whose token mixer is
-// one of latent attention (a compressed key/value cache), a gated delta rule with per-channel decay, or a Mamba-2 state-space layer, each
-// beside a routed mixture-of-experts feed-forward, with an optional looped block that re-injects the embedding.  Every size and constant
-// is read from the checkpoint folder's config.json; nothing here is specific to one checkpoint.
+// hybrid_config.hpp — configuration of the hybrid decoder family: a stack of parallel-residual layers whose token mixer is one of latent
+// attention (a compressed key/value cache), a gated delta rule with per-channel decay, a Mamba-2 state-space layer, or windowed attention
+// over cached keys and values (sliding window with optional kept first tokens, one or two score maps per head, optional sink, output gate,
+// optionally reading another layer's cache), each beside a routed mixture-of-experts feed-forward, with an optional looped block that
+// re-injects the embedding.  Two designs are registered: "Ratasun" (one weight-only layer norm per layer, sigmoid group-limited router, SwiGLU
+// experts) and "Zurevik" (two RMS norms per layer, softmax over the chosen router logits, squared-ReLU experts, scaled embedding, soft-capped
+// logits).  Every size and constant is read from the checkpoint folder's config.json; nothing here is specific to one checkpoint.
 #pragma once
 #include <cstdio>
 #include <fstream>
@@ -14,12 +17,17 @@
 
 namespace oa {
 
-enum HyMixer : int { HY_LATENT_ATTENTION = 0, HY_CHANNEL_DELTA = 1, HY_MAMBA2 = 2 };
+enum HyMixer : int { HY_LATENT_ATTENTION = 0, HY_CHANNEL_DELTA = 1, HY_MAMBA2 = 2, HY_WINDOW_ATTENTION = 3 };
+enum HyNorm : int { HY_LAYER_NORM = 0, HY_RMS_NORM = 1 };
+enum HyRouterKind : int { HY_ROUTER_SIGMOID_GROUPS = 0, HY_ROUTER_SOFTMAX_CHOSEN = 1 };   // weights: sigmoid scores renormalised and scaled / softmax over the chosen logits
+enum HyExpertAct : int { HY_EXPERT_SWIGLU = 0, HY_EXPERT_RELU2 = 1 };                       // down(silu(gate x) * up x) / down(relu(up x)^2)
+enum HyGate : int { HY_GATE_NONE = 0, HY_GATE_CHANNEL = 1, HY_GATE_HEAD = 2 };
 
 struct HyMoe {
     bool present = false;
     int experts = 0, top = 0, groups = 1, keep = 1, ff = 0;
     float scale = 1.f;
+    int router = HY_ROUTER_SIGMOID_GROUPS, act = HY_EXPERT_SWIGLU;
 };
 
 struct HyLayer {
@@ -29,15 +37,25 @@ struct HyLayer {
     // mamba2:           heads x vdim inner channels, state N, groups of B/C, norm_groups, conv taps
     int heads = 0, kv_heads = 0, dim = 0, rot_dim = 0, vdim = 0, kv_rank = 0, rot_dims = 0, conv = 0, state = 0, groups = 1, norm_groups = 1;
     float rot_base = 10000.f, scale = 1.f;
+    // window attention: heads query heads on kv_heads key/value heads, `maps` score maps per head (2 = differential: q and k hold [map 1 | map 2] per
+    // head, out = a1 - lambda a2, unit RMS per head, times 1 - diff); position i sees j <= i with i - j < window or j < keep_first; qk_norm: RMS
+    // norm of every query / key map with a weight shared by heads and maps; bias: q/k/v projection biases; sink: a learned logit per head in
+    // the softmax denominator only; gate: sigmoid output gate per channel or per head; kv_from >= 0: keys and values of that layer's cache
+    int maps = 1, window = 0, keep_first = 0, qk_norm = 0, bias = 0, sink = 0, gate = HY_GATE_NONE, kv_from = -1;
+    float diff = 0.f;
     HyMoe moe;
 };
 
-struct HyRun { int layer = 0, pass = -1; bool first_of_pass = false; int cache_idx = -1, state_idx = -1; };   // one execution of a layer (a looped layer runs once per pass)
+struct HyRun { int layer = 0, pass = -1; bool first_of_pass = false; int cache_idx = -1, state_idx = -1; bool cache_owner = false; };   // one execution of a layer (a looped layer runs once per pass)
 
 struct HybridConfig {
     std::string dir;                      // checkpoint folder (config.json [+ model.safetensors]; without the latter the weights are seeded)
     int width = 0, vocab = 0;
     float eps = 1e-6f, logit_scale = 1.f;
+    std::string arch = "ratasun";        // registry key of the design
+    int norm = HY_LAYER_NORM;             // the layers' (and the final) norm
+    bool two_norms = false;               // mixer and feed-forward each read their own norm of the same residual
+    float embed_scale = 1.f, logit_softcap = 0.f;      // x = embed[token] * scale; logits <- cap * tanh(logits / cap) (0: none)
     std::vector<HyLayer> layers;
     int loop_start = 0, loop_stop = 0, loop_times = 0;    // times == 0: no looped block
     std::vector<HyRun> runs;
@@ -67,10 +85,23 @@ struct HybridConfig {
         return j.str("architecture");
     }
 
+    // the model registry of this family: config.json's "architecture" -> registry key ("" = not one of ours)
+    static std::string registry_key(const std::string& architecture) {
+        if (architecture == "Ratasun") return "ratasun";
+        if (architecture == "Zurevik") return "zurevik";
+        return "";
+    }
+
     static HybridConfig load(const std::string& dir) {
         Json j; std::string err;
         if (!parse_json(read_file(dir + "/config.json"), j, err)) throw std::runtime_error("config.json: " + err);
         HybridConfig c; c.dir = dir;
+        c.arch = registry_key(j.str("architecture"));
+        if (c.arch.empty()) throw std::runtime_error("config.json: unknown architecture '" + j.str("architecture") + "'");
+        const bool zu = c.arch == "zurevik";
+        if (zu) { c.norm = HY_RMS_NORM; c.two_norms = true; }
+        if (const Json* e = j.get("embedding")) if (e->t == Json::Obj && e->get("scale")) c.embed_scale = (float)num(*e, "scale", "embedding");
+        if (j.get("logit_softcap") && j.get("logit_softcap")->t == Json::Num) c.logit_softcap = (float)num(j, "logit_softcap", "the model");
         c.width = integer(j, "width", "the model"); c.vocab = integer(j, "vocab", "the model");
         c.eps = (float)num(obj(j, "norm", "the model"), "eps", "norm");
         c.logit_scale = j.get("logit_scale") ? (float)num(j, "logit_scale", "the model") : 1.f;
@@ -96,14 +127,37 @@ struct HybridConfig {
                 l.heads = integer(m, "heads", type.c_str()); l.vdim = integer(m, "vdim", type.c_str()); l.state = integer(m, "state", type.c_str());
                 l.groups = integer(m, "groups", type.c_str()); l.norm_groups = integer(m, "norm_groups", type.c_str()); l.conv = integer(m, "conv", type.c_str());
                 if (l.groups <= 0 || l.heads % l.groups || l.norm_groups <= 0 || (l.heads * l.vdim) % l.norm_groups) throw std::runtime_error("config.json: groups must divide heads, norm_groups the inner size");
+            } else if (type == "attention" || type == "attention_2") {
+                // "attention": differential (two score maps), query/key norm, kept first tokens, gate per channel;
+                // "attention_2": one map, projection biases, a sink per head, gate per head, optionally another layer's keys and values
+                const bool diff = type == "attention";
+                l.type = HY_WINDOW_ATTENTION;
+                l.heads = integer(m, "heads", type.c_str()); l.kv_heads = integer(m, "kv_heads", type.c_str()); l.dim = integer(m, "dim", type.c_str());
+                l.vdim = integer(m, "vdim", type.c_str()); l.scale = (float)num(m, "scale", type.c_str());
+                const Json& mk = obj(m, "mask", type.c_str());
+                l.window = integer(mk, "size", "mask");
+                if (mk.get("keep_first") && mk.get("keep_first")->t == Json::Num) l.keep_first = integer(mk, "keep_first", "mask");
+                l.maps = diff ? 2 : 1; l.qk_norm = diff; l.bias = !diff; l.sink = !diff; l.gate = diff ? HY_GATE_CHANNEL : HY_GATE_HEAD;
+                if (diff) l.diff = (float)num(m, "diff", type.c_str());
+                if (!diff && m.get("kv_from") && m.get("kv_from")->t == Json::Num) {
+                    l.kv_from = integer(m, "kv_from", type.c_str());
+                    if (l.kv_from < 0 || l.kv_from >= (int)c.layers.size()) throw std::runtime_error("config.json: kv_from must name an earlier layer");
+                    const HyLayer& src = c.layers[l.kv_from];
+                    if (src.type != HY_WINDOW_ATTENTION || src.kv_from >= 0 || src.maps != l.maps || src.kv_heads != l.kv_heads || src.dim != l.dim || src.vdim != l.vdim)
+                        throw std::runtime_error("config.json: kv_from must name a layer with keys and values of its own and of this layer's sizes");
+                }
+                if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.dim <= 0 || l.window < 1 || l.keep_first < 0) throw std::runtime_error("config.json: bad attention sizes");
             } else throw std::runtime_error("config.json: unknown layer type '" + type + "'");
-            if (l.heads <= 0 || l.vdim <= 0 || (l.type != HY_LATENT_ATTENTION && (l.conv < 1 || l.conv > 16))) throw std::runtime_error("config.json: bad mixer sizes");
+            const bool recurrent = l.type == HY_CHANNEL_DELTA || l.type == HY_MAMBA2;
+            if (l.heads <= 0 || l.vdim <= 0 || (recurrent && (l.conv < 1 || l.conv > 16))) throw std::runtime_error("config.json: bad mixer sizes");
             const Json* mj = lj.get("mlp");
             if (mj && mj->t == Json::Obj) {
                 if (mj->str("kind") != "moe") throw std::runtime_error("config.json: unknown mlp kind '" + mj->str("kind") + "'");
                 const Json& r = obj(*mj, "router", "mlp");
                 l.moe.present = true; l.moe.ff = integer(obj(*mj, "expert", "mlp"), "ff", "expert");
-                l.moe.experts = integer(r, "experts", "router"); l.moe.top = integer(r, "top", "router"); l.moe.scale = (float)num(r, "scale", "router");
+                l.moe.experts = integer(r, "experts", "router"); l.moe.top = integer(r, "top", "router");
+                if (zu) { l.moe.router = HY_ROUTER_SOFTMAX_CHOSEN; l.moe.act = HY_EXPERT_RELU2; }
+                else l.moe.scale = (float)num(r, "scale", "router");
                 if (const Json* g = r.get("groups")) if (g->t == Json::Obj) { l.moe.groups = integer(*g, "count", "groups"); l.moe.keep = integer(*g, "keep", "groups"); }
                 if (l.moe.groups <= 0 || l.moe.experts % l.moe.groups || l.moe.keep <= 0 || l.moe.keep > l.moe.groups || l.moe.top <= 0 ||
                     l.moe.top > l.moe.keep * (l.moe.experts / l.moe.groups) || l.moe.top > 32 || l.moe.experts > 1024)
@@ -119,7 +173,13 @@ struct HybridConfig {
         // expand the schedule of layer executions: each execution owns its cache (attention) or state (recurrent mixers)
         auto add = [&](int layer, int pass, bool first) {
             HyRun r; r.layer = layer; r.pass = pass; r.first_of_pass = first;
-            if (c.layers[layer].type == HY_LATENT_ATTENTION) r.cache_idx = c.n_caches++; else r.state_idx = c.n_states++;
+            const HyLayer& l = c.layers[layer];
+            if (l.type == HY_WINDOW_ATTENTION && l.kv_from >= 0) {          // the cache of the (only) execution of the layer it reads
+                for (const HyRun& o : c.runs) if (o.layer == l.kv_from) r.cache_idx = o.cache_idx;
+                if (r.cache_idx < 0 || (c.loop_times > 0 && layer >= c.loop_start && layer < c.loop_stop) || (c.loop_times > 0 && l.kv_from >= c.loop_start && l.kv_from < c.loop_stop))
+                    throw std::runtime_error("config.json: a layer that reads another layer's cache cannot be part of a looped block");
+            } else if (l.type == HY_LATENT_ATTENTION || l.type == HY_WINDOW_ATTENTION) { r.cache_idx = c.n_caches++; r.cache_owner = true; }
+            else r.state_idx = c.n_states++;
             c.runs.push_back(r);
         };
         for (int i = 0; i < (int)c.layers.size();) {

@@ -6,49 +6,13 @@
 #include <utility>
 
 #include "hybrid_kernels.hpp"
-#include "kernels.hpp"
-#include "common.cuh"
+#include "hybrid_common.cuh"
 
 namespace oa {
 
 namespace {
 
-__device__ __forceinline__ float ldf(const float* p) { return *p; }
-__device__ __forceinline__ float ldf(const __nv_bfloat16* p) { return __bfloat162float(*p); }
-__device__ __forceinline__ void stf(float* p, float v) { *p = v; }
-__device__ __forceinline__ void stf(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
-__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
-__device__ __forceinline__ float siluf_(float z) { return z / (1.0f + expf(-z)); }
-__device__ __forceinline__ float softplusf_(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-// sum over the block (blockDim.x <= 1024, a multiple of 32); every thread gets the result
-__device__ __forceinline__ float block_sum(float v, float* red) {
-    v = warp_sum(v);
-    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
-    __syncthreads();
-    if (l == 0) red[w] = v;
-    __syncthreads();
-    float t = 0.f;
-    for (int i = 0; i < nw; ++i) t += red[i];
-    return t;
-}
-
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
-}
-
-// Every kernel of this file opens with HY_PDL(): it lets the next kernel of the stream become resident early (programmatic dependent
-// launch) and then waits until every predecessor grid has completed and its memory is visible — nothing is read or written before that, so
-// the kernels stay strictly ordered; what overlaps is only the launch latency and the ramp of the next grid.
-#define HY_PDL() do { griddep_launch(); griddep_wait(); } while (0)
-template <typename... KArgs, typename... Args>
-cudaError_t launch_plain(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
-    return launch_k(kern, grid, block, smem, st, std::forward<Args>(args)...);
-}
+using namespace hyk;
 
 // ---------------------------------------------------------------------------------------------------------------------------------
 // GEMM: 64 x 64 tile, 16-wide k slices, 256 threads x (4 x 4) outputs.  The k order of every output is fixed (0..K-1), so a row's result
@@ -100,10 +64,10 @@ __global__ void __launch_bounds__(256) hy_gemm_kernel(const TA* __restrict__ A, 
 }
 
 template <typename TA>
-__global__ void hy_embed_kernel(const int32_t* ids, const TA* table, float* x, float* x0, int T, int W, int vocab) {
+__global__ void hy_embed_kernel(const int32_t* ids, const TA* table, float* x, float* x0, int T, int W, int vocab, float scale) {
     HY_PDL();
     const int t = blockIdx.x; int id = ids[t]; id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
-    for (int c = threadIdx.x; c < W; c += blockDim.x) { const float v = ldf(table + (long long)id * W + c); x[(long long)t * W + c] = v; x0[(long long)t * W + c] = v; }
+    for (int c = threadIdx.x; c < W; c += blockDim.x) { const float v = ldf(table + (long long)id * W + c) * scale; x[(long long)t * W + c] = v; if (x0) x0[(long long)t * W + c] = v; }
 }
 template <typename TA>
 __global__ void hy_concat_kernel(const float* x, const float* x0, TA* cat, int T, int W) {
@@ -927,6 +891,31 @@ __global__ void __launch_bounds__(128) hy_moe_router_kernel(HyRouter m, const fl
     if (lane < m.top) { idx[(long long)t * m.top + lane] = my_e; wgt[(long long)t * m.top + lane] = mine / (sum + 1e-20f) * m.scale; }
 }
 
+// one warp per token: z = logits + bias, the `top` largest logits (ties -> lower index), weights = softmax over the chosen ones
+__global__ void __launch_bounds__(128) hy_moe_router_softmax_kernel(HyRouter m, const float* logits, int ldz, const float* bias, int32_t* idx, float* wgt, int T) {
+    HY_PDL();
+    extern __shared__ float sm[];
+    const int E = m.experts, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = blockIdx.x * 4 + warp;
+    if (t >= T) return;
+    float* ch = sm + warp * E;
+    for (int e = lane; e < E; e += 32) ch[e] = logits[(long long)t * ldz + e] + (bias ? bias[e] : 0.f);
+    __syncwarp();
+    float mine = -INFINITY, first = 0.f; int my_e = 0;      // lane k keeps choice k; choice 0 is the largest logit
+    for (int k = 0; k < m.top; ++k) {
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) { const float v = ch[e]; if (v > bv || (v == bv && e < bi && v != -INFINITY)) { bv = v; bi = e; } }
+        warp_argmax(bv, bi);
+        if (bi >= E) bi = 0;
+        if (k == 0) first = bv;
+        if (lane == k) { my_e = bi; mine = bv; }
+        if (lane == 0) ch[bi] = -INFINITY;
+        __syncwarp();
+    }
+    const float p = lane < m.top ? expf(mine - first) : 0.f;
+    const float sum = warp_sum(p);
+    if (lane < m.top) { idx[(long long)t * m.top + lane] = my_e; wgt[(long long)t * m.top + lane] = p / sum; }
+}
+
 template <typename TA>
 __global__ void __launch_bounds__(256) hy_moe_gate_up_kernel(const TA* h, int ldh, const TA* gu, int ldw, int W, int ff, int ffp, const int32_t* idx, int top, TA* act) {
     HY_PDL();
@@ -940,6 +929,23 @@ __global__ void __launch_bounds__(256) hy_moe_gate_up_kernel(const TA* h, int ld
         for (int i = lane; i < W; i += 32) { const float x = ldf(hr + i); g = fmaf(x, ldf(wg + i), g); u = fmaf(x, ldf(wu + i), u); }
         g = warp_sum(g); u = warp_sum(u);
         v = siluf_(g) * u;
+    }
+    if (lane == 0) stf(act + (long long)row * ffp + f, v);
+}
+// experts without a gate: act = relu(up h)^2, up rows [E][ffp][ldw]
+template <typename TA>
+__global__ void __launch_bounds__(256) hy_moe_up_relu2_kernel(const TA* h, int ldh, const TA* up, int ldw, int W, int ff, int ffp, const int32_t* idx, int top, TA* act) {
+    HY_PDL();
+    const int row = blockIdx.x, t = row / top, e = idx[row], warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int f = blockIdx.y * 8 + warp;
+    if (f >= ffp) return;
+    float v = 0.f;
+    if (f < ff) {
+        const TA* wu = up + ((long long)e * ffp + f) * ldw; const TA* hr = h + (long long)t * ldh;
+        float u = 0.f;
+        for (int i = lane; i < W; i += 32) u = fmaf(ldf(hr + i), ldf(wu + i), u);
+        u = fmaxf(warp_sum(u), 0.f);
+        v = u * u;
     }
     if (lane == 0) stf(act + (long long)row * ffp + f, v);
 }
@@ -1053,12 +1059,16 @@ __global__ void hy_gather_rows_f32_kernel(const float* x, const int32_t* rows, f
     const int i = blockIdx.x;
     for (int c = threadIdx.x; c < W; c += blockDim.x) out[(long long)i * W + c] = x[(long long)rows[i] * W + c];
 }
-__global__ void __launch_bounds__(256) hy_argmax_rows_kernel(const float* logits, int V, int32_t* out_ids) {
+__global__ void __launch_bounds__(256) hy_argmax_rows_kernel(float* logits, int V, float softcap, int32_t* out_ids) {
     HY_PDL();
     __shared__ float bv[8]; __shared__ int bi[8];
-    const float* lr = logits + (long long)blockIdx.x * V;
+    float* lr = logits + (long long)blockIdx.x * V;
     float v = -INFINITY; int i = 0x7fffffff;
-    for (int c = threadIdx.x; c < V; c += blockDim.x) { const float f = lr[c]; if (f > v || (f == v && c < i)) { v = f; i = c; } }
+    for (int c = threadIdx.x; c < V; c += blockDim.x) {
+        float f = lr[c];
+        if (softcap > 0.f) { f = softcap * tanhf(f / softcap); lr[c] = f; }
+        if (f > v || (f == v && c < i)) { v = f; i = c; }
+    }
     warp_argmax(v, i);
     if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = v; bi[threadIdx.x >> 5] = i; }
     __syncthreads();
@@ -1095,9 +1105,9 @@ cudaError_t hy_gemm(bool f32, int mode, const void* A, int lda, const void* B, i
     return f32 ? gemm_t<float>(mode, A, lda, B, ldb, C, ldc, M, N, K, bias, alpha, batch, sA, sB, sC, s)
                : gemm_t<bf>(mode, A, lda, B, ldb, C, ldc, M, N, K, bias, alpha, batch, sA, sB, sC, s);
 }
-cudaError_t hy_embed(bool f32, const int32_t* ids, const void* table, float* x, float* x0, int T, int W, int vocab, cudaStream_t s) {
-    return f32 ? launch_plain(hy_embed_kernel<float>, dim3(T), dim3(128), 0, s, ids, (const float*)table, x, x0, T, W, vocab)
-               : launch_plain(hy_embed_kernel<bf>, dim3(T), dim3(128), 0, s, ids, (const bf*)table, x, x0, T, W, vocab);
+cudaError_t hy_embed(bool f32, const int32_t* ids, const void* table, float* x, float* x0, int T, int W, int vocab, float scale, cudaStream_t s) {
+    return f32 ? launch_plain(hy_embed_kernel<float>, dim3(T), dim3(128), 0, s, ids, (const float*)table, x, x0, T, W, vocab, scale)
+               : launch_plain(hy_embed_kernel<bf>, dim3(T), dim3(128), 0, s, ids, (const bf*)table, x, x0, T, W, vocab, scale);
 }
 cudaError_t hy_concat(bool f32, const float* x, const float* x0, void* cat, int T, int W, cudaStream_t s) {
     return f32 ? launch_plain(hy_concat_kernel<float>, dim3(T), dim3(128), 0, s, x, x0, (float*)cat, T, W)
@@ -1265,8 +1275,15 @@ cudaError_t hy_moe_router(const HyRouter& m, const float* logits, int ldz, const
     const size_t smem = (size_t)4 * (2 * m.experts + m.groups) * 4;
     return launch_plain(hy_moe_router_kernel, dim3((T + 3) / 4), dim3(128), smem, s, m, logits, ldz, correction, idx, wgt, T);
 }
-cudaError_t hy_moe_gate_up(bool f32, const void* h, int ldh, const void* gu, int ldw, int W, int ff, int ffp, const int32_t* idx, int top, void* act, int T, cudaStream_t s) {
+cudaError_t hy_moe_router_softmax(const HyRouter& m, const float* logits, int ldz, const float* bias, int32_t* idx, float* wgt, int T, cudaStream_t s) {
+    if (m.top > 32) return cudaErrorInvalidValue;
+    return launch_plain(hy_moe_router_softmax_kernel, dim3((T + 3) / 4), dim3(128), (size_t)4 * m.experts * 4, s, m, logits, ldz, bias, idx, wgt, T);
+}
+cudaError_t hy_moe_gate_up(bool f32, int relu2, const void* h, int ldh, const void* gu, int ldw, int W, int ff, int ffp, const int32_t* idx, int top, void* act, int T, cudaStream_t s) {
     dim3 grid(T * top, (ffp + 7) / 8);
+    if (relu2)
+        return f32 ? launch_plain(hy_moe_up_relu2_kernel<float>, grid, dim3(256), 0, s, (const float*)h, ldh, (const float*)gu, ldw, W, ff, ffp, idx, top, (float*)act)
+                   : launch_plain(hy_moe_up_relu2_kernel<bf>, grid, dim3(256), 0, s, (const bf*)h, ldh, (const bf*)gu, ldw, W, ff, ffp, idx, top, (bf*)act);
     return f32 ? launch_plain(hy_moe_gate_up_kernel<float>, grid, dim3(256), 0, s, (const float*)h, ldh, (const float*)gu, ldw, W, ff, ffp, idx, top, (float*)act)
                : launch_plain(hy_moe_gate_up_kernel<bf>, grid, dim3(256), 0, s, (const bf*)h, ldh, (const bf*)gu, ldw, W, ff, ffp, idx, top, (bf*)act);
 }
@@ -1297,9 +1314,9 @@ cudaError_t hy_gather_rows_f32(const float* x, const int32_t* rows, float* out, 
     if (n <= 0) return cudaSuccess;
     return launch_plain(hy_gather_rows_f32_kernel, dim3(n), dim3(128), 0, s, x, rows, out, W);
 }
-cudaError_t hy_argmax_rows(const float* logits, int n, int V, int32_t* out_ids, cudaStream_t s) {
+cudaError_t hy_argmax_rows(float* logits, int n, int V, float softcap, int32_t* out_ids, cudaStream_t s) {
     if (n <= 0) return cudaSuccess;
-    return launch_plain(hy_argmax_rows_kernel, dim3(n), dim3(256), 0, s, logits, V, out_ids);
+    return launch_plain(hy_argmax_rows_kernel, dim3(n), dim3(256), 0, s, logits, V, softcap, out_ids);
 }
 cudaError_t hy_add_rowvec(float* x, const float* v, int T, int W, cudaStream_t s) { return launch_plain(hy_add_rowvec_kernel, dim3(T), dim3(256), 0, s, x, v, W); }
 

@@ -1,6 +1,8 @@
-// hybrid_kernels.hpp — launch API of the kernels behind the hybrid decoder family (hybrid_kernels.cu): layer norm, latent attention over a
-// paged latent cache, causal short convolutions with carried tails, the linear recurrences (gated delta rule with per-channel decay, Mamba-2),
-// gated group norms, the grouped-limited sigmoid router and the routed experts.  Each mechanism takes its sizes and constants as arguments.
+// hybrid_kernels.hpp — launch API of the kernels behind the hybrid decoder family (hybrid_kernels.cu, hybrid_window.cu): layer norm and RMS
+// norm, latent attention over a paged latent cache, windowed attention over paged keys and values (sliding window, kept first tokens,
+// differential maps, sink, output gates), causal short convolutions with carried tails, the linear recurrences (gated delta rule with
+// per-channel decay, Mamba-2), gated group norms, the routers (group-limited sigmoid; softmax over the chosen logits) and the routed experts
+// (SwiGLU; squared ReLU).  Each mechanism takes its sizes and constants as arguments.
 //
 // `f32` selects the activation / matrix element type: false = bf16 storage with fp32 accumulation, true = everything in fp32.  What must be
 // fp32 in both modes (residual stream, norms, softmax, router, recurrent state, decays, gates of a recurrence) always is.
@@ -28,11 +30,29 @@ enum HyGemmMode : int { HY_STORE = 0, HY_STORE_F32 = 1, HY_ACC_F32 = 2 };
 cudaError_t hy_gemm(bool f32, int mode, const void* A, int lda, const void* B, int ldb, void* C, int ldc, int M, int N, int K, const float* bias,
                     float alpha, int batch, long long sA, long long sB, long long sC, cudaStream_t s);
 
-cudaError_t hy_embed(bool f32, const int32_t* ids, const void* table, float* x, float* x0, int T, int W, int vocab, cudaStream_t s);
+// x[t] = table[ids[t]] * scale (fp32); x0 (optional) keeps a copy for a looped block's re-injection
+cudaError_t hy_embed(bool f32, const int32_t* ids, const void* table, float* x, float* x0, int T, int W, int vocab, float scale, cudaStream_t s);
 // cat[t] = [x[t] ; x0[t]] in the activation type (input of the looped block's re-injection projection)
 cudaError_t hy_concat(bool f32, const float* x, const float* x0, void* cat, int T, int W, cudaStream_t s);
 // out[t] = (x[t] - mean) / sqrt(var + eps) * w   (optionally of the rows `rows[i]` only)
 cudaError_t hy_layernorm(bool f32, const float* x, const int32_t* rows, const float* w, void* out, int ldo, int T, int W, float eps, cudaStream_t s);
+
+// out1[t] = x[r] / sqrt(mean(x[r]^2) + eps) * w1, and out2 likewise with w2 when given (r = rows[t] or t): the two norms of a layer whose
+// mixer and feed-forward read separate norms of the same residual, or a single RMS norm
+cudaError_t hy_rmsnorm_pair(bool f32, const float* x, const int32_t* rows, const float* w1, void* out1, const float* w2, void* out2, int ldo, int T, int W, float eps, cudaStream_t s);
+
+// Windowed attention over cached keys and values.  A cache row holds one token: [kv_heads x maps x dim keys | kv_heads x vdim values].
+// Position i sees j <= i with i - j < window or j < keep_first.  maps = 2: differential attention, out = (a1 - lambda a2) / rms(.) * out_scale
+// per head.  gate: 0 none, 1 sigmoid(gate[t, head * vdim + c]), 2 sigmoid(gate[t, head]).  sink (per head, or null) joins the denominator only.
+struct HyWinAttn { int heads, kv_heads, dim, vdim, maps, window, keep_first, qk_norm, gate; float scale, lambda, out_scale; };
+bool hy_win_supported(const HyWinAttn& a);
+// q [T, ldq] (head by head, map by map): RMS-normed in place with q_norm_w when qk_norm; k / v [T, ldkv] (null: this layer reads a cache
+// another layer fills): keys normed alike with k_norm_w, both stored at cache row slots[t]
+cudaError_t hy_win_prep(bool f32, const HyWinAttn& a, void* q, int ldq, const void* k, const void* v, int ldkv, const float* q_norm_w, const float* k_norm_w, float eps, void* cache,
+                        const HyRows& r, cudaStream_t s);
+// plain form (any sizes, both element types; prefill rows and decoding rows alike): out[t, head * vdim ..] in the activation type
+cudaError_t hy_win_attention(bool f32, const HyWinAttn& a, const void* q, int ldq, const void* cache, const float* sink, const void* gate, int ldg, void* out, int ldo, float eps,
+                             const HyRows& r, cudaStream_t s);
 
 struct HyLatentAttn {             // sizes of one latent-attention layer
     int heads, dim, rot_dim, vdim, kv_rank, rot_dims; float scale;
@@ -94,13 +114,15 @@ cudaError_t hy_recurrence(bool delta, const float* qq, const float* kk, const fl
 cudaError_t hy_gated_norm(bool f32, const float* o, int C, int group, const float* w, int wlen, const void* gate, int ld_gate, int gate_before, int act,
                           const float* skip, int skip_block, const void* xs, int ld_xs, void* out, int ld_out, float eps, int T, cudaStream_t s);
 
-struct HyRouter { int experts, top, groups, keep; float scale; };
+struct HyRouter { int experts, top, groups, keep; float scale; int kind; };     // kind 0: the sigmoid router below; 1: hy_moe_router_softmax
 // sigmoid router over fp32 logits [T, ldz] with a selection-only correction and group-limited choice: a group's score is the sum of its two
 // largest corrected scores, only the best `keep` groups compete; idx[t, top], wgt[t, top] = chosen uncorrected sigmoids / their sum * scale
 cudaError_t hy_moe_router(const HyRouter& m, const float* logits, int ldz, const float* correction, int32_t* idx, float* wgt, int T, cudaStream_t s);
-// routed experts, one (token, choice) at a time (decode-sized batches and the fp32 mode).  gu: [E][2 ffp][ldw] with gate / up rows interleaved in
-// blocks of 16, down: [E][W][ffp]; act: [T * top, ffp]
-cudaError_t hy_moe_gate_up(bool f32, const void* h, int ldh, const void* gu, int ldw, int W, int ff, int ffp, const int32_t* idx, int top, void* act, int T, cudaStream_t s);
+// router whose weights are the softmax over the chosen logits only: z = logits + bias (fp32), the `top` largest (ties -> lower index), wgt = softmax of those
+cudaError_t hy_moe_router_softmax(const HyRouter& m, const float* logits, int ldz, const float* bias, int32_t* idx, float* wgt, int T, cudaStream_t s);
+// routed experts, one (token, choice) at a time (decode-sized batches and the fp32 mode).  relu2 == 0: SwiGLU, gu: [E][2 ffp][ldw] with gate / up
+// rows interleaved in blocks of 16; relu2 == 1: act = relu(up h)^2, gu: [E][ffp][ldw] (up rows only).  down: [E][W][ffp]; act: [T * top, ffp]
+cudaError_t hy_moe_gate_up(bool f32, int relu2, const void* h, int ldh, const void* gu, int ldw, int W, int ff, int ffp, const int32_t* idx, int top, void* act, int T, cudaStream_t s);
 cudaError_t hy_moe_down(bool f32, const void* act, const void* down, int W, int ffp, const int32_t* idx, const float* wgt, int top, float* x, int T, cudaStream_t s);
 
 // grouped (tensor-core) expert path: rows sorted by expert into 128-row tiles
@@ -112,7 +134,8 @@ cudaError_t hy_moe_gather(const void* h, int ldh, int W, const int32_t* row_src,
 cudaError_t hy_moe_combine(const float* y, int ldy, const int32_t* dst_of, const float* wgt, int top, float* x, int W, int T, cudaStream_t s);
 
 cudaError_t hy_gather_rows_f32(const float* x, const int32_t* rows, float* out, int n, int W, cudaStream_t s);
-cudaError_t hy_argmax_rows(const float* logits, int n, int V, int32_t* out_ids, cudaStream_t s);
+// softcap > 0: logits <- softcap * tanh(logits / softcap), in place, before the arg-max (ties -> lowest id)
+cudaError_t hy_argmax_rows(float* logits, int n, int V, float softcap, int32_t* out_ids, cudaStream_t s);
 // x[t, :] += v[:]
 cudaError_t hy_add_rowvec(float* x, const float* v, int T, int W, cudaStream_t s);
 

@@ -141,8 +141,38 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
         const HyLayer& l = hc_.layers[li]; LayerW& w = lw_[li];
         const std::string p = "l" + std::to_string(li) + ".", mx = p + "mix.";
         w.norm1 = upload_f32(vec(p + "norm1", W, 1.f, 0.1f));
+        if (hc_.two_norms && l.moe.present) w.norm2 = upload_f32(vec(p + "norm2", W, 1.f, 0.1f));
         HostMat in; in.K = W; int rows = 0;
-        if (l.type == HY_LATENT_ATTENTION) {
+        if (l.type == HY_WINDOW_ATTENTION) {
+            // fused input projection [q | k | v | gate] (k, v only where the layer fills a cache of its own), each segment on a multiple of 8 rows
+            const int qd = l.heads * l.maps * l.dim, kd = l.kv_heads * l.maps * l.dim, vd = l.kv_heads * l.vdim;
+            const int gd = l.gate == HY_GATE_CHANNEL ? l.heads * l.vdim : l.gate == HY_GATE_HEAD ? l.heads : 0;
+            if (!hy_win_supported(HyWinAttn{l.heads, l.kv_heads, l.dim, l.vdim, l.maps, l.window, l.keep_first, l.qk_norm, l.gate, l.scale, 0.f, 1.f}))
+                throw std::runtime_error("config.json: attention sizes beyond what the kernels hold (vdim <= 256)");
+            std::vector<float> bias;
+            auto seg = [&](const char* nm, int n, bool biased) -> int {
+                while (rows % 8) { in.v.resize(in.v.size() + W, 0.f); ++rows; }
+                const int off = rows;
+                append_rows(in.v, rows, W, tensor(mx + nm, n, W).v, n, 1);
+                if (l.bias) { bias.resize(off, 0.f); std::vector<float> b = biased ? vec(mx + nm + ".b", n, 0.f, 0.2f) : std::vector<float>(n, 0.f); bias.insert(bias.end(), b.begin(), b.end()); }
+                return off;
+            };
+            w.off_a = seg("q", qd, true);
+            if (l.kv_from < 0) { w.off_b = seg("k", kd, true); w.off_c = seg("v", vd, true); }
+            if (gd) w.off_d = seg("g", gd, false);
+            if (l.bias) { bias.resize(up8(rows), 0.f); w.in_bias = upload_f32(bias); w.in_bias_act = upload_act(bias); }
+            if (l.qk_norm) { w.q_norm = upload_f32(vec(mx + "q.norm", l.dim, 1.f, 0.1f)); w.k_norm = upload_f32(vec(mx + "k.norm", l.dim, 1.f, 0.1f)); }
+            if (l.sink) w.sink = upload_f32(vec(mx + "sink", l.heads, 0.f, 1.f));
+            if (l.maps == 2) {        // lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff: one number per layer, fp32
+                const float sp = 1.0f / std::sqrt((float)l.dim);
+                std::vector<float> q1 = vec(mx + "lq1", l.dim, 0.f, sp), k1 = vec(mx + "lk1", l.dim, 0.f, sp), q2 = vec(mx + "lq2", l.dim, 0.f, sp), k2 = vec(mx + "lk2", l.dim, 0.f, sp);
+                float d1 = 0.f, d2 = 0.f;
+                for (int i = 0; i < l.dim; ++i) { d1 += q1[i] * k1[i]; d2 += q2[i] * k2[i]; }
+                w.lambda = std::exp(d1) - std::exp(d2) + l.diff;
+            }
+            w.o = upload_mat(tensor(mx + "o", W, l.heads * l.vdim));
+            max_mix = std::max(max_mix, l.heads * l.vdim);
+        } else if (l.type == HY_LATENT_ATTENTION) {
             const int qd = l.heads * (l.dim + l.rot_dim), E = l.kv_rank + l.rot_dim;
             append_rows(in.v, rows, W, tensor(mx + "q", qd, W).v, qd, 1); w.off_a = 0;
             while (rows % 8) { in.v.resize(in.v.size() + W, 0.f); ++rows; }
@@ -223,15 +253,23 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
         if (l.moe.present) {
             const HyMoe& m = l.moe; const std::string mp = p + "mlp.";
             w.router = upload_mat(tensor(mp + "router", m.experts, W));
-            w.correction = upload_f32(vec(mp + "correction", m.experts, 0.f, 0.05f));
+            if (m.router == HY_ROUTER_SOFTMAX_CHOSEN) w.router_bias = upload_f32(vec(mp + "router.b", m.experts, 0.f, 0.05f));
+            else w.correction = upload_f32(vec(mp + "correction", m.experts, 0.f, 0.05f));
             w.ffp = up16(m.ff);
-            std::vector<float> gu((size_t)m.experts * 2 * w.ffp * Wld_, 0.f), dn((size_t)m.experts * W * w.ffp, 0.f);
+            // first-stage rows per expert: SwiGLU experts hold gate and up rows interleaved in blocks of 16, gate-less experts their up rows
+            const int rows1 = m.act == HY_EXPERT_RELU2 ? w.ffp : 2 * w.ffp;
+            std::vector<float> gu((size_t)m.experts * rows1 * Wld_, 0.f), dn((size_t)m.experts * W * w.ffp, 0.f);
             for (int e = 0; e < m.experts; ++e) {
                 const std::string ep = mp + "e" + std::to_string(e) + ".";
-                HostMat g = tensor(ep + "gate", m.ff, W), u = tensor(ep + "up", m.ff, W), d = tensor(ep + "down", W, m.ff);
-                for (int f = 0; f < m.ff; ++f) {
-                    const size_t pg = ((size_t)e * 2 * w.ffp + (size_t)(f >> 4) * 32 + (f & 15)) * Wld_;
-                    std::memcpy(&gu[pg], &g.v[(size_t)f * W], (size_t)W * 4); std::memcpy(&gu[pg + (size_t)16 * Wld_], &u.v[(size_t)f * W], (size_t)W * 4);
+                HostMat u = tensor(ep + "up", m.ff, W), d = tensor(ep + "down", W, m.ff);
+                if (m.act == HY_EXPERT_RELU2) {
+                    for (int f = 0; f < m.ff; ++f) std::memcpy(&gu[((size_t)e * w.ffp + f) * Wld_], &u.v[(size_t)f * W], (size_t)W * 4);
+                } else {
+                    HostMat g = tensor(ep + "gate", m.ff, W);
+                    for (int f = 0; f < m.ff; ++f) {
+                        const size_t pg = ((size_t)e * 2 * w.ffp + (size_t)(f >> 4) * 32 + (f & 15)) * Wld_;
+                        std::memcpy(&gu[pg], &g.v[(size_t)f * W], (size_t)W * 4); std::memcpy(&gu[pg + (size_t)16 * Wld_], &u.v[(size_t)f * W], (size_t)W * 4);
+                    }
                 }
                 for (int n = 0; n < W; ++n) std::memcpy(&dn[((size_t)e * W + n) * w.ffp], &d.v[(size_t)n * m.ff], (size_t)m.ff * 4);
             }
@@ -240,7 +278,7 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
                 w.moe_tc = true;
                 for (int i = 0; i < 2; ++i) {
                     const uint32_t bn = i ? 256 : 128;
-                    if (make_tmap_bf16_2d(&w.tm_gu[i], w.gu, (uint64_t)m.experts * 2 * w.ffp, (uint64_t)Wld_, (uint64_t)Wld_, bn, 64) != 0 ||
+                    if (make_tmap_bf16_2d(&w.tm_gu[i], w.gu, (uint64_t)m.experts * rows1, (uint64_t)Wld_, (uint64_t)Wld_, bn, 64) != 0 ||
                         make_tmap_bf16_2d(&w.tm_down[i], w.down, (uint64_t)m.experts * W, (uint64_t)w.ffp, (uint64_t)w.ffp, bn, 64) != 0) w.moe_tc = false;
                 }
             }
@@ -255,6 +293,7 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
     const size_t MR = (size_t)MR_;
     x_ = (float*)dmalloc(MR * W * 4); x0_ = (float*)dmalloc(MR * W * 4);
     cat_ = dmalloc(MR * 2 * Wld_ * es_); h_ = dmalloc(MR * Wld_ * es_);
+    if (hc_.two_norms) h2_ = dmalloc(MR * Wld_ * es_);
     ld_proj_ = max_in; ld_p2_ = up8(max_p2); ld_conv_ = up8(max_conv); ld_mix_ = up8(max_mix);
     proj_ = dmalloc(MR * ld_proj_ * es_); p2_ = dmalloc(MR * ld_p2_ * es_); conv_ = dmalloc(MR * ld_conv_ * es_); mix_ = dmalloc(MR * ld_mix_ * es_);
     q_abs_ = (float*)dmalloc(MR * max_qabs * 4); lat_ = dmalloc(MR * up8(max_lat) * es_);
@@ -277,7 +316,7 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
 
     // ---- paged latent cache + state slots ----
     size_t page_bytes = 0;
-    for (const HyRun& r : hc_.runs) if (r.cache_idx >= 0) { const HyLayer& l = hc_.layers[r.layer]; page_bytes += (size_t)64 * (l.kv_rank + l.rot_dim) * es_; }
+    for (const HyRun& r : hc_.runs) if (r.cache_owner) page_bytes += (size_t)64 * cache_row_width(hc_.layers[r.layer]) * es_;
     if (opt.num_pages > 0) num_pages = opt.num_pages;
     else {
         size_t free_b = 0, total_b = 0;
@@ -292,8 +331,8 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
     state_slots = hc_.n_states > 0 ? opt.max_batch : 0;
     for (const HyRun& r : hc_.runs) {
         const HyLayer& l = hc_.layers[r.layer];
-        if (r.cache_idx >= 0) { const size_t b = (size_t)num_pages * 64 * (l.kv_rank + l.rot_dim) * es_; caches_[r.cache_idx] = dmalloc(b); kv_pool_bytes += b; }
-        else {
+        if (r.cache_owner) { const size_t b = (size_t)num_pages * 64 * cache_row_width(l) * es_; caches_[r.cache_idx] = dmalloc(b); kv_pool_bytes += b; }
+        else if (r.state_idx >= 0) {
             const int sd = l.type == HY_CHANNEL_DELTA ? l.dim : l.state;
             states_[r.state_idx] = (float*)dmalloc((size_t)state_slots * l.heads * sd * l.vdim * 4);
             tails_[r.state_idx] = dmalloc((size_t)state_slots * std::max(1, l.conv - 1) * lw_[r.layer].conv_ch * es_);
@@ -333,41 +372,44 @@ static int pick_tile_n(int M, int N, int sms) {
 }
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-void HybridModel::gemm(int mode, const void* A, int lda, const Mat& B, void* C, int ldc, int M, const float* bias, float alpha) {
+void HybridModel::gemm(int mode, const void* A, int lda, const Mat& B, void* C, int ldc, int M, const float* bias, float alpha, const void* bias_act) {
     // bf16: the framework's tcgen05 tile GEMM (TMA operands, fp32 accumulator in TMEM) wherever pitches and pointers fit its 16-byte rules;
     // a bf16 store may write the columns up to N rounded up to 8 (every such output has that room), an fp32 output needs N itself to fit
     bool tc = B.tc && !f32_ && lda % 8 == 0 && aligned16(A) && lda >= B.ld;
-    if (mode == HY_STORE) tc = tc && ldc % 8 == 0 && aligned16(C) && !bias && alpha == 1.f;
+    if (mode == HY_STORE) tc = tc && ldc % 8 == 0 && aligned16(C) && (!bias || (bias_act && aligned16(bias_act))) && alpha == 1.f;     // a bias in the activation type, padded to N rounded up to 8
     else tc = tc && B.N % 8 == 0 && ldc % 4 == 0 && aligned16(C) && (!bias || aligned16(bias));
     CUtensorMap tmA;
     if (tc && make_tmap_bf16_2d(&tmA, A, (uint64_t)M, (uint64_t)B.ld, (uint64_t)lda, 128, 64) != 0) tc = false;
     if (!tc) { cuda_check(hy_gemm(f32_, mode, A, lda, B.p, B.ld, C, ldc, M, B.N, B.K, bias, alpha, 1, 0, 0, 0, stream), "gemm"); return; }
     GemmParams g{}; g.M = M; g.N = up8(B.N); g.K = B.ld;
     const int bn = pick_tile_n(M, g.N, sm_count);
-    if (mode == HY_STORE) { g.out = C; g.ldo = ldc; cuda_check(launch_gemm(&tmA, &B.tm[bn == 32 ? 0 : bn == 64 ? 1 : bn == 128 ? 2 : 3], g, EPI_STORE, bn, stream), "gemm (tcgen05)"); return; }
+    if (mode == HY_STORE) { g.out = C; g.ldo = ldc; g.bias = bias ? bias_act : nullptr; cuda_check(launch_gemm(&tmA, &B.tm[bn == 32 ? 0 : bn == 64 ? 1 : bn == 128 ? 2 : 3], g, EPI_STORE, bn, stream), "gemm (tcgen05)"); return; }
     g.f32_out = reinterpret_cast<float*>(C); g.ldf = ldc; g.f32_accumulate = mode == HY_ACC_F32; g.alpha = alpha; g.bias_f32 = bias;
     cuda_check(launch_gemm(&tmA, &B.tm[bn == 32 ? 0 : bn == 64 ? 1 : bn == 128 ? 2 : 3], g, EPI_F32, bn, stream), "gemm (tcgen05, fp32 out)");
 }
 
-void HybridModel::moe(const LayerW& w, const HyLayer& l, const HyRows& r, const std::function<void(int)>& MARK) {
+void HybridModel::moe(const LayerW& w, const HyLayer& l, const void* h_in, const HyRows& r, const std::function<void(int)>& MARK) {
     const HyMoe& m = l.moe; const int W = hc_.width, T = r.T;
-    HyRouter hr{m.experts, m.top, m.groups, m.keep, m.scale};
+    const bool relu2 = m.act == HY_EXPERT_RELU2; const int rows1 = relu2 ? w.ffp : 2 * w.ffp;
+    HyRouter hr{m.experts, m.top, m.groups, m.keep, m.scale, m.router};
     // router logits: bf16 (or fp32) inputs, exact products, fp32 accumulation and output
-    gemm(HY_STORE_F32, h_, Wld_, w.router, rlog_, m.experts, T, nullptr, 1.f);
-    cuda_check(hy_moe_router(hr, rlog_, m.experts, w.correction, idx_, wgt_, T, stream), "router"); MARK(12);
+    gemm(HY_STORE_F32, h_in, Wld_, w.router, rlog_, m.experts, T, nullptr, 1.f);
+    if (m.router == HY_ROUTER_SOFTMAX_CHOSEN) cuda_check(hy_moe_router_softmax(hr, rlog_, m.experts, w.router_bias, idx_, wgt_, T, stream), "router");
+    else cuda_check(hy_moe_router(hr, rlog_, m.experts, w.correction, idx_, wgt_, T, stream), "router");
+    MARK(12);
     if (w.moe_tc && T >= opt.hy_moe_grouped_rows) {
         // prefill-sized batches: rows sorted by expert into 128-row tiles, two grouped tcgen05 GEMMs (SwiGLU in the first one's epilogue),
         // then each token adds its choices' rows in choice order
         const int bound = std::min(max_tiles_, (T * m.top + 127) / 128 + std::min(m.experts, T * m.top));
         cuda_check(hy_moe_plan(idx_, T, m.top, m.experts, tile_expert_, row_src_, n_tiles_, dst_of_, bound, stream), "expert plan");
-        cuda_check(hy_moe_gather(h_, Wld_, Wld_, row_src_, n_tiles_, m.top, moe_a_, bound, stream), "expert gather"); MARK(16);
+        cuda_check(hy_moe_gather(h_in, Wld_, Wld_, row_src_, n_tiles_, m.top, moe_a_, bound, stream), "expert gather"); MARK(16);
         CUtensorMap tmA, tmB;
         if (make_tmap_bf16_2d(&tmA, moe_a_, (uint64_t)bound * 128, (uint64_t)Wld_, (uint64_t)Wld_, 128, 64) != 0 ||
             make_tmap_bf16_2d(&tmB, act_, (uint64_t)bound * 128, (uint64_t)w.ffp, (uint64_t)w.ffp, 128, 64) != 0) throw std::runtime_error("tensor map for the expert activations failed");
-        GemmParams g{}; g.M = bound * 128; g.N = 2 * w.ffp; g.K = Wld_; g.out = act_; g.ldo = w.ffp;
-        g.m_tile_group = tile_expert_; g.n_m_tiles = n_tiles_; g.group_rows = 2 * w.ffp;
-        const int bn1 = 2 * w.ffp >= 256 ? 256 : 128;
-        cuda_check(launch_gemm(&tmA, &w.tm_gu[bn1 == 256], g, EPI_SWIGLU, bn1, stream), "experts gate/up (grouped tcgen05)"); MARK(17);
+        GemmParams g{}; g.M = bound * 128; g.N = rows1; g.K = Wld_; g.out = act_; g.ldo = w.ffp; g.store_act = relu2 ? 1 : 0;
+        g.m_tile_group = tile_expert_; g.n_m_tiles = n_tiles_; g.group_rows = rows1;
+        const int bn1 = rows1 >= 256 ? 256 : 128;
+        cuda_check(launch_gemm(&tmA, &w.tm_gu[bn1 == 256], g, relu2 ? EPI_STORE : EPI_SWIGLU, bn1, stream), "experts first stage (grouped tcgen05)"); MARK(17);
         GemmParams d{}; d.M = bound * 128; d.N = W; d.K = w.ffp; d.f32_out = moe_y_; d.ldf = W; d.alpha = 1.f;
         d.m_tile_group = tile_expert_; d.n_m_tiles = n_tiles_; d.group_rows = W;
         const int bn2 = W >= 256 ? 256 : 128;
@@ -375,14 +417,15 @@ void HybridModel::moe(const LayerW& w, const HyLayer& l, const HyRows& r, const 
         cuda_check(hy_moe_combine(moe_y_, W, dst_of_, wgt_, m.top, x_, W, T, stream), "expert combine"); MARK(19);
         return;
     }
-    cuda_check(hy_moe_gate_up(f32_, h_, Wld_, w.gu, Wld_, W, m.ff, w.ffp, idx_, m.top, act_, T, stream), "experts gate/up");
+    cuda_check(hy_moe_gate_up(f32_, relu2, h_in, Wld_, w.gu, Wld_, W, m.ff, w.ffp, idx_, m.top, act_, T, stream), "experts first stage");
     cuda_check(hy_moe_down(f32_, act_, w.down, W, w.ffp, idx_, wgt_, m.top, x_, T, stream), "experts down"); MARK(13);
 }
 
 const char* HybridModel::kt_name(int id) const {
     static const char* n[32] = {"h2d+embed", "layer_norm", "in_proj_gemm", "latent_absorb+up_gemm", "latent_cache_write", "latent_attention", "conv", "recurrence_prep",
                                 "recurrence", "gated_norm", "low_rank_gemm", "out_proj_gemm", "router", "experts_per_token", "loop_in", "head+argmax",
-                                "expert_plan+gather", "expert_gate_up_gemm", "expert_down_gemm", "expert_combine", "context_gather+kv_up_gemm", "attention_prefill_form", "", "", "", "", "", "", "", "", "", ""};
+                                "expert_plan+gather", "expert_gate_up_gemm", "expert_down_gemm", "expert_combine", "context_gather+kv_up_gemm", "attention_prefill_form", "rms_norm", "window_qk_norm+cache_write",
+                                "window_attention", "", "", "", "", "", "", ""};
     return n[id & 31];
 }
 
@@ -472,7 +515,7 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
         cudaEventRecord(ev_all[ek++], stream);
     }
     const std::function<void(int)> MARK = [&](int id) { if (profile_all && ek < ev_all.size()) { ev_ids[ek] = id; cudaEventRecord(ev_all[ek++], stream); } };
-    cuda_check(hy_embed(f32_, d_meta_ + o_tok, embed_, x_, x0_, T, W, V, stream), "embed"); MARK(0);
+    cuda_check(hy_embed(f32_, d_meta_ + o_tok, embed_, x_, hc_.loop_times > 0 ? x0_ : nullptr, T, W, V, hc_.embed_scale, stream), "embed"); MARK(0);
     auto at = [&](void* base, size_t elems) -> void* { return reinterpret_cast<char*>(base) + elems * es_; };
     for (const HyRun& run : hc_.runs) {
         const HyLayer& l = hc_.layers[run.layer]; const LayerW& w = lw_[run.layer];
@@ -480,9 +523,17 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
             cuda_check(hy_concat(f32_, x_, x0_, cat_, T, W, stream), "concat");
             gemm(HY_STORE_F32, cat_, 2 * W, loop_in_, x_, W, T, loop_step_ + (size_t)run.pass * W, 1.f); MARK(14);
         }
-        cuda_check(hy_layernorm(f32_, x_, nullptr, w.norm1, h_, Wld_, T, W, hc_.eps, stream), "layer norm"); MARK(1);
-        gemm(HY_STORE, h_, Wld_, w.in, proj_, ld_proj_, T, nullptr, 1.f); MARK(2);
-        if (l.type == HY_LATENT_ATTENTION) {
+        if (hc_.norm == HY_RMS_NORM) { cuda_check(hy_rmsnorm_pair(f32_, x_, nullptr, w.norm1, h_, w.norm2, w.norm2 ? h2_ : nullptr, Wld_, T, W, hc_.eps, stream), "rms norm"); MARK(22); }
+        else { cuda_check(hy_layernorm(f32_, x_, nullptr, w.norm1, h_, Wld_, T, W, hc_.eps, stream), "layer norm"); MARK(1); }
+        gemm(HY_STORE, h_, Wld_, w.in, proj_, ld_proj_, T, w.in_bias, 1.f, w.in_bias_act); MARK(2);
+        if (l.type == HY_WINDOW_ATTENTION) {
+            const HyWinAttn a{l.heads, l.kv_heads, l.dim, l.vdim, l.maps, l.window, l.keep_first, l.qk_norm, l.gate, l.scale, w.lambda, 1.f - l.diff};
+            const bool own = run.cache_owner;
+            cuda_check(hy_win_prep(f32_, a, at(proj_, w.off_a), ld_proj_, own ? at(proj_, w.off_b) : nullptr, own ? at(proj_, w.off_c) : nullptr, ld_proj_, w.q_norm, w.k_norm, hc_.eps,
+                                   caches_[run.cache_idx], r, stream), "query / key norm + cache write"); MARK(23);
+            cuda_check(hy_win_attention(f32_, a, at(proj_, w.off_a), ld_proj_, caches_[run.cache_idx], w.sink, l.gate ? at(proj_, w.off_d) : nullptr, ld_proj_, mix_, ld_mix_, hc_.eps,
+                                        r, stream), "windowed attention"); MARK(24);
+        } else if (l.type == HY_LATENT_ATTENTION) {
             const HyLatentAttn a{l.heads, l.dim, l.rot_dim, l.vdim, l.kv_rank, l.rot_dims, l.scale};
             const int E = l.kv_rank + l.rot_dim;
             const TileList& tl = tile_lists[run.layer];
@@ -534,7 +585,7 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
                                      hc_.eps, T, stream), "gated norm"); MARK(9);
         }
         gemm(HY_ACC_F32, mix_, ld_mix_, w.o, x_, W, T, nullptr, 1.f); MARK(11);
-        if (l.moe.present) moe(w, l, r, MARK);
+        if (l.moe.present) moe(w, l, w.norm2 ? h2_ : h_, r, MARK);
         if (capture_layers) {
             cuda_check(cudaStreamSynchronize(stream), "capture sync");
             const size_t n0 = capture_layers->size(); capture_layers->resize(n0 + (size_t)T * W);
@@ -546,11 +597,12 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
         capture_layers = nullptr;
     }
     if (NS > 0) {
-        cuda_check(hy_layernorm(f32_, x_, d_meta_ + o_samp, final_norm_, hs_, Wld_, NS, W, hc_.eps, stream), "final norm");
+        if (hc_.norm == HY_RMS_NORM) cuda_check(hy_rmsnorm_pair(f32_, x_, d_meta_ + o_samp, final_norm_, hs_, nullptr, nullptr, Wld_, NS, W, hc_.eps, stream), "final norm");
+        else cuda_check(hy_layernorm(f32_, x_, d_meta_ + o_samp, final_norm_, hs_, Wld_, NS, W, hc_.eps, stream), "final norm");
         if (!logits_out && NS > opt.max_batch) throw std::runtime_error("forward: more sampled rows than sequences need a caller's logits buffer");
         float* lg = logits_out ? logits_out : logits_;
         gemm(HY_STORE_F32, hs_, Wld_, head_, lg, V, NS, nullptr, hc_.logit_scale);
-        cuda_check(hy_argmax_rows(lg, NS, V, d_out_ids_, stream), "argmax");
+        cuda_check(hy_argmax_rows(lg, NS, V, hc_.logit_softcap, d_out_ids_, stream), "soft cap + argmax");
         cuda_check(cudaMemcpyAsync(h_out_ids, d_out_ids_, (size_t)NS * 4, cudaMemcpyDeviceToHost, stream), "ids D2H");
         d2h_bytes += (size_t)NS * 4; MARK(15);
     }
@@ -561,7 +613,7 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
 }
 
 std::unique_ptr<ModelBase> make_model(const ModelConfig& cfg, const EngineOptions& opt) {
-    if (cfg.arch == "ratasun") return std::unique_ptr<ModelBase>(new HybridModel(cfg, opt));
+    if (cfg.hybrid) return std::unique_ptr<ModelBase>(new HybridModel(cfg, opt));        // "ratasun", "zurevik": one class, configured by the design's traits
     if (opt.f32) throw std::runtime_error("the Llama-family models run in bf16 only; float32 is available for the hybrid family");
     return std::unique_ptr<ModelBase>(new DeviceModel(cfg, opt));
 }

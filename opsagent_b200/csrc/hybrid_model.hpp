@@ -1,7 +1,7 @@
 // hybrid_model.hpp — device-resident model of the hybrid decoder family (configuration: hybrid_config.hpp, kernels: hybrid_kernels.hpp).
 // It plugs into the same scheduler as the Llama-family DeviceModel: rows of a step arrive as a StepInput (prefill chunks and single decode
-// tokens alike), attention layers keep their compressed keys in the engine's 64-token pages, recurrent layers keep an fp32 state and their
-// convolution tails in the sequence's state slot.
+// tokens alike), attention layers keep their compressed keys (latent attention) or their keys and values (windowed attention) in the engine's
+// 64-token pages, recurrent layers keep an fp32 state and their convolution tails in the sequence's state slot.
 #pragma once
 #include <functional>
 #include <string>
@@ -29,8 +29,11 @@ private:
     };
     struct HostMat { int N = 0, K = 0; std::vector<float> v; };
     struct LayerW {
-        float* norm1 = nullptr;
+        float *norm1 = nullptr, *norm2 = nullptr;      // norm2: the feed-forward's own norm (designs with two norms per layer)
         Mat in, a2, g2, o, router, kv_up;
+        float* in_bias = nullptr; void* in_bias_act = nullptr;      // bias of the fused input projection (fp32, and in the activation type for the tensor-core epilogue)
+        float *q_norm = nullptr, *k_norm = nullptr, *sink = nullptr, lambda = 0.f;     // windowed attention
+        float* router_bias = nullptr;
         int off_a = 0, off_b = 0, off_c = 0, off_d = 0;   // column offsets of the fused input projection's segments (see hybrid_model.cpp)
         int a_rank = 0, g_rank = 0;
         void *uk_t = nullptr, *uv = nullptr; float* dkv_norm = nullptr; int rope = -1;      // latent attention
@@ -48,8 +51,9 @@ private:
     Mat upload_mat(const HostMat& m);
     HostMat tensor(const std::string& name, int N, int K);                // checkpoint tensor (or seeded values) as fp32 [N, K]; K == 0: any width
     std::vector<float> vec(const std::string& name, int n, float init_mean, float init_spread);
-    void gemm(int mode, const void* A, int lda, const Mat& B, void* C, int ldc, int M, const float* bias, float alpha);
-    void moe(const LayerW& w, const HyLayer& l, const HyRows& r, const std::function<void(int)>& mark);
+    void gemm(int mode, const void* A, int lda, const Mat& B, void* C, int ldc, int M, const float* bias, float alpha, const void* bias_act = nullptr);
+    void moe(const LayerW& w, const HyLayer& l, const void* h, const HyRows& r, const std::function<void(int)>& mark);
+    int cache_row_width(const HyLayer& l) const { return l.type == HY_WINDOW_ATTENTION ? l.kv_heads * (l.maps * l.dim + l.vdim) : l.kv_rank + l.rot_dim; }
 
     HybridConfig hc_; bool f32_ = false; size_t es_ = 2;
     struct SafeTensorsHolder; SafeTensorsHolder* st_ = nullptr;
@@ -62,7 +66,7 @@ private:
     // activations
     float *x_ = nullptr, *x0_ = nullptr, *q_abs_ = nullptr, *qq_ = nullptr, *kk_ = nullptr, *vv_ = nullptr, *dec_ = nullptr, *beta_ = nullptr, *rec_ = nullptr, *wgt_ = nullptr,
           *logits_ = nullptr, *moe_y_ = nullptr, *rlog_ = nullptr;
-    void *cat_ = nullptr, *h_ = nullptr, *proj_ = nullptr, *p2_ = nullptr, *conv_ = nullptr, *lat_ = nullptr, *mix_ = nullptr, *act_ = nullptr, *hs_ = nullptr, *moe_a_ = nullptr;
+    void *cat_ = nullptr, *h_ = nullptr, *h2_ = nullptr, *proj_ = nullptr, *p2_ = nullptr, *conv_ = nullptr, *lat_ = nullptr, *mix_ = nullptr, *act_ = nullptr, *hs_ = nullptr, *moe_a_ = nullptr;
     int ld_proj_ = 0, ld_p2_ = 0, ld_conv_ = 0, ld_mix_ = 0;
     int32_t *idx_ = nullptr, *d_out_ids_ = nullptr, *tile_expert_ = nullptr, *row_src_ = nullptr, *n_tiles_ = nullptr, *dst_of_ = nullptr; int max_tiles_ = 0;
     int32_t* h_meta_buf_[2] = {nullptr, nullptr}; cudaEvent_t meta_ev_[2] = {nullptr, nullptr}; int meta_idx_ = 0;
