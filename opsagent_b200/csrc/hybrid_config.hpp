@@ -146,7 +146,7 @@ struct HybridConfig {
                     if (src.type != HY_WINDOW_ATTENTION || src.kv_from >= 0 || src.maps != l.maps || src.kv_heads != l.kv_heads || src.dim != l.dim || src.vdim != l.vdim)
                         throw std::runtime_error("config.json: kv_from must name a layer with keys and values of its own and of this layer's sizes");
                 }
-                if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.dim <= 0 || l.window < 1 || l.keep_first < 0) throw std::runtime_error("config.json: bad attention sizes");
+                if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.dim <= 0 || l.window < 1 || l.keep_first < 0 || l.vdim > 256 || l.dim > 1024) throw std::runtime_error("config.json: bad attention sizes");
             } else throw std::runtime_error("config.json: unknown layer type '" + type + "'");
             const bool recurrent = l.type == HY_CHANNEL_DELTA || l.type == HY_MAMBA2;
             if (l.heads <= 0 || l.vdim <= 0 || (recurrent && (l.conv < 1 || l.conv > 16))) throw std::runtime_error("config.json: bad mixer sizes");
