@@ -54,6 +54,14 @@ cudaError_t hy_win_prep(bool f32, const HyWinAttn& a, void* q, int ldq, const vo
 cudaError_t hy_win_attention(bool f32, const HyWinAttn& a, const void* q, int ldq, const void* cache, const float* sink, const void* gate, int ldg, void* out, int ldo, float eps,
                              const HyRows& r, cudaStream_t s);
 
+// tensor-core form (bf16; dim a multiple of 16 up to 128, vdim 16 / 32 / 64 / 96 / 128), for prompt portions and decoding rows alike: a tile =
+// 64 consecutive (row, head-of-the-group) pairs of one sequence starting at pair tile_q0 (pair p = row p / group, head p % group of the
+// CTA's key/value head, group = heads / kv_heads); grid = tiles x kv_heads.  The host lists the tiles of a step.
+constexpr int HY_WIN_TILE_QUERIES = 64;
+bool hy_win_mma_supported(const HyWinAttn& a);
+cudaError_t hy_win_attention_mma(const HyWinAttn& a, const void* q, int ldq, const void* cache, const float* sink, const void* gate, int ldg, void* out, int ldo, float eps,
+                                 const HyRows& r, const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles, cudaStream_t s);
+
 struct HyLatentAttn {             // sizes of one latent-attention layer
     int heads, dim, rot_dim, vdim, kv_rank, rot_dims; float scale;
 };

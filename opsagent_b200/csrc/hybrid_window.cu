@@ -158,6 +158,189 @@ __global__ void __launch_bounds__(128) hy_win_attention_kernel(HyWinAttn a, cons
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------------
+// Tensor-core form (bf16; dim a multiple of 16 up to 128, vdim 16 / 32 / 64 / 96 / 128): one CTA owns 64 query slots — consecutive
+// (row, head) pairs of ONE sequence and ONE key/value head, so a prompt portion brings 64 / group rows per CTA and a decoding row its whole
+// group — and streams that head's cached keys and values in 32-row tiles through a cp.async double buffer, straight from the pages.  Only
+// tiles that hold a visible key are visited: the kept first positions below the window of the tile's first row, then the window.  Both
+// score maps of a differential head are computed from the same key tile and weigh the same value tile; S = Q K^T and O += P V are
+// mma.sync m16n8k16 products, the softmax is online in fp32 registers with the mask per query position.  The epilogue finishes the head in
+// registers: sink into the denominator, a1 - lambda a2, unit RMS over the head's channels (a quad shuffle), gate, bf16 store into the
+// output projection's input.
+// ---------------------------------------------------------------------------------------------------------------------------------
+constexpr int WIN_MQ = 64, WIN_KT = 32;
+template <int MAPS, int NVB>
+__global__ void __launch_bounds__(128) hy_win_attention_mma_kernel(HyWinAttn a, const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ cache,
+                                                                   const float* __restrict__ sink, const __nv_bfloat16* __restrict__ gate, int ldg,
+                                                                   __nv_bfloat16* __restrict__ out, int ldo, float eps, HyRows r, const int32_t* __restrict__ tile_seq,
+                                                                   const int32_t* __restrict__ tile_q0) {
+    HY_PDL();
+    extern __shared__ __align__(16) uint8_t win_smem[];
+    constexpr int VD = NVB * 8, VP = VD + 8;
+    const int D = a.dim, QD = MAPS * D, QP = QD + 8, HG = a.heads / a.kv_heads, g = blockIdx.y;
+    const int KW = a.kv_heads * QD, CW = KW + a.kv_heads * VD;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(win_smem);      // [64][QP]
+    __nv_bfloat16* Ks = Qs + WIN_MQ * QP;                                // [2][32][QP]
+    __nv_bfloat16* Vs = Ks + 2 * WIN_KT * QP;                            // [2][32][VP]
+    int* qpos = reinterpret_cast<int*>(Vs + 2 * WIN_KT * VP);            // [64]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int seq = tile_seq[blockIdx.x], q0 = tile_q0[blockIdx.x];
+    const int row0 = r.seq_row0[seq], len = r.seq_row0[seq + 1] - row0;
+    const int nq = min(WIN_MQ, len * HG - q0);
+    for (int idx = tid; idx < WIN_MQ * (QD / 8); idx += 128) {
+        const int qi = idx / (QD / 8), c = idx - qi * (QD / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (qi < nq) v = *reinterpret_cast<const uint4*>(q + (long long)(row0 + (q0 + qi) / HG) * ldq + (long long)(g * HG + (q0 + qi) % HG) * QD + c * 8);
+        *reinterpret_cast<uint4*>(Qs + qi * QP + c * 8) = v;
+    }
+    for (int qi = tid; qi < WIN_MQ; qi += 128) qpos[qi] = qi < nq ? r.positions[row0 + (q0 + qi) / HG] : -1;
+    const int pos_min = r.positions[row0 + q0 / HG], pos_max = r.positions[row0 + (q0 + nq - 1) / HG];
+    const int lo_min = max(0, pos_min - a.window + 1);
+    const int win_t0 = lo_min / WIN_KT, n_kt = pos_max / WIN_KT + 1;
+    const int n_keep = min((min(a.keep_first, lo_min) + WIN_KT - 1) / WIN_KT, win_t0);      // tiles of kept first positions that lie wholly below the window's first tile
+    const int n_it = n_keep + (n_kt - win_t0);
+    const int32_t* bt = r.block_tables + (long long)seq * r.max_pages_per_seq;
+    auto load_tile = [&](int it, int buf) {
+        const int kt = it < n_keep ? it : win_t0 + (it - n_keep);
+        const int kc = QD / 8, vc = VD / 8;
+        for (int idx = tid; idx < WIN_KT * (kc + vc); idx += 128) {
+            const int j = idx / (kc + vc), c = idx - j * (kc + vc), key = kt * WIN_KT + j;
+            __nv_bfloat16* dst = c < kc ? Ks + (buf * WIN_KT + j) * QP + c * 8 : Vs + (buf * WIN_KT + j) * VP + (c - kc) * 8;
+            if (key <= pos_max) {
+                const __nv_bfloat16* row = cache + ((long long)bt[key >> 6] * 64 + (key & 63)) * CW;
+                cp_async16(dst, c < kc ? row + (long long)g * QD + c * 8 : row + KW + (long long)g * VD + (c - kc) * 8);
+            } else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float o[MAPS][NVB][4];
+    float m_lo[MAPS], m_hi[MAPS], l_lo[MAPS], l_hi[MAPS];
+#pragma unroll
+    for (int mp = 0; mp < MAPS; ++mp) {
+        m_lo[mp] = m_hi[mp] = -INFINITY; l_lo[mp] = l_hi[mp] = 0.f;
+#pragma unroll
+        for (int i = 0; i < NVB; ++i) { o[mp][i][0] = o[mp][i][1] = o[mp][i][2] = o[mp][i][3] = 0.f; }
+    }
+    const float qscale = a.scale * 1.4426950408889634f;
+    const bool active = 16 * warp < nq;
+    load_tile(0, 0);
+    for (int it = 0; it < n_it; ++it) {
+        if (it + 1 < n_it) { load_tile(it + 1, (it + 1) & 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        if (active) {
+            const int kt = it < n_keep ? it : win_t0 + (it - n_keep);
+            const __nv_bfloat16* Kb = Ks + (it & 1) * WIN_KT * QP; const __nv_bfloat16* Vb = Vs + (it & 1) * WIN_KT * VP;
+            const int p_lo = qpos[16 * warp + (lane >> 2)], p_hi = qpos[16 * warp + (lane >> 2) + 8];
+            uint32_t pa[MAPS][2][4];        // P of this tile as A fragments, per map and 16-key half
+#pragma unroll
+            for (int mp = 0; mp < MAPS; ++mp) {
+                float s[4][4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+                const uint32_t qa = smem_u32(Qs + (16 * warp + (lane & 15)) * QP + mp * D + (lane >> 4) * 8);
+                const uint32_t ka = smem_u32(Kb + ((lane >> 4) * 8 + (lane & 7)) * QP + mp * D + ((lane >> 3) & 1) * 8);
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                    ldmatrix_x4(qa + ks * 32, a0, a1, a2, a3);
+                    ldmatrix_x4(ka + ks * 32, b0, b1, b2, b3);
+                    mma_bf16_16816(s[0], a0, a1, a2, a3, b0, b1); mma_bf16_16816(s[1], a0, a1, a2, a3, b2, b3);
+                    ldmatrix_x4(ka + 16 * QP * 2 + ks * 32, b0, b1, b2, b3);
+                    mma_bf16_16816(s[2], a0, a1, a2, a3, b0, b1); mma_bf16_16816(s[3], a0, a1, a2, a3, b2, b3);
+                }
+                float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+                for (int nb = 0; nb < 4; ++nb)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int key = kt * WIN_KT + nb * 8 + (lane & 3) * 2 + (c & 1), p = c < 2 ? p_lo : p_hi;
+                        const bool vis = key <= p && (p - key < a.window || key < a.keep_first);
+                        s[nb][c] = vis ? s[nb][c] * qscale : -INFINITY;
+                        if (c < 2) mx_lo = fmaxf(mx_lo, s[nb][c]); else mx_hi = fmaxf(mx_hi, s[nb][c]);
+                    }
+                mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1)); mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+                mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)); mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+                // a tile may hold no visible key for some of its rows (their window starts later): the running maximum then stays -inf
+                const float n_lo = fmaxf(m_lo[mp], mx_lo), n_hi = fmaxf(m_hi[mp], mx_hi);
+                const float b_lo = n_lo == -INFINITY ? 0.f : n_lo, b_hi = n_hi == -INFINITY ? 0.f : n_hi;
+                const float c_lo = exp2f(m_lo[mp] - b_lo), c_hi = exp2f(m_hi[mp] - b_hi);
+                m_lo[mp] = n_lo; m_hi[mp] = n_hi;
+                float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+                for (int nb = 0; nb < 4; ++nb) {
+                    s[nb][0] = exp2f(s[nb][0] - b_lo); s[nb][1] = exp2f(s[nb][1] - b_lo); s[nb][2] = exp2f(s[nb][2] - b_hi); s[nb][3] = exp2f(s[nb][3] - b_hi);
+                    sum_lo += s[nb][0] + s[nb][1]; sum_hi += s[nb][2] + s[nb][3];
+                }
+                l_lo[mp] = l_lo[mp] * c_lo + sum_lo; l_hi[mp] = l_hi[mp] * c_hi + sum_hi;
+#pragma unroll
+                for (int i = 0; i < NVB; ++i) { o[mp][i][0] *= c_lo; o[mp][i][1] *= c_lo; o[mp][i][2] *= c_hi; o[mp][i][3] *= c_hi; }
+#pragma unroll
+                for (int kk = 0; kk < 2; ++kk) {
+                    pa[mp][kk][0] = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]); pa[mp][kk][1] = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
+                    pa[mp][kk][2] = pack_bf16x2(s[2 * kk + 1][0], s[2 * kk + 1][1]); pa[mp][kk][3] = pack_bf16x2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+                }
+            }
+            const uint32_t va = smem_u32(Vb + (((lane >> 3) & 1) * 8 + (lane & 7)) * VP + (lane >> 4) * 8);
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk)
+#pragma unroll
+                for (int np = 0; np < NVB / 2; ++np) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(va + kk * 16 * VP * 2 + np * 32, b0, b1, b2, b3);      // one value fragment serves both maps
+#pragma unroll
+                    for (int mp = 0; mp < MAPS; ++mp) {
+                        mma_bf16_16816(o[mp][2 * np], pa[mp][kk][0], pa[mp][kk][1], pa[mp][kk][2], pa[mp][kk][3], b0, b1);
+                        mma_bf16_16816(o[mp][2 * np + 1], pa[mp][kk][0], pa[mp][kk][1], pa[mp][kk][2], pa[mp][kk][3], b2, b3);
+                    }
+                }
+        }
+        __syncthreads();
+    }
+    if (!active) return;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int qi = 16 * warp + (lane >> 2) + half * 8;
+        const bool ok = qi < nq;                       // every lane stays for the quad shuffles
+        const int row = row0 + (q0 + (ok ? qi : 0)) / HG, head = g * HG + (q0 + (ok ? qi : 0)) % HG;
+        float f[MAPS];
+#pragma unroll
+        for (int mp = 0; mp < MAPS; ++mp) {
+            float l = half ? l_hi[mp] : l_lo[mp]; const float m = half ? m_hi[mp] : m_lo[mp];
+            l += __shfl_xor_sync(0xffffffffu, l, 1); l += __shfl_xor_sync(0xffffffffu, l, 2);
+            float up = 1.f;
+            if (sink) {                                // the sink joins the denominator (scores are kept in base-2 units)
+                const float s2 = sink[head] * 1.4426950408889634f, M = fmaxf(m, s2);
+                up = m == -INFINITY ? 0.f : exp2f(m - M); l = l * up + exp2f(s2 - M);
+            }
+            f[mp] = l > 0.f ? up / l : 0.f;
+        }
+        float y[NVB][2], ss = 0.f;
+#pragma unroll
+        for (int nb = 0; nb < NVB; ++nb)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float v = o[0][nb][half * 2 + e] * f[0];
+                if (MAPS == 2) v -= a.lambda * (o[MAPS - 1][nb][half * 2 + e] * f[MAPS - 1]);
+                y[nb][e] = v; ss = fmaf(v, v, ss);
+            }
+        float post = 1.f;
+        if (MAPS == 2) {
+            ss += __shfl_xor_sync(0xffffffffu, ss, 1); ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+            post = a.out_scale / sqrtf(ss / (float)VD + eps);
+        }
+        if (!ok) continue;
+        if (a.gate == 2) post *= sigmoidf_(__bfloat162float(gate[(long long)row * ldg + head]));
+        __nv_bfloat16* dst = out + (long long)row * ldo + (long long)head * VD + (lane & 3) * 2;
+        const __nv_bfloat16* gp = gate + (long long)row * ldg + (long long)head * VD + (lane & 3) * 2;
+#pragma unroll
+        for (int nb = 0; nb < NVB; ++nb) {
+            float y0 = y[nb][0] * post, y1 = y[nb][1] * post;
+            if (a.gate == 1) { const uint32_t gg = *reinterpret_cast<const uint32_t*>(gp + nb * 8); y0 *= sigmoidf_(bf16lo(gg)); y1 *= sigmoidf_(bf16hi(gg)); }
+            *reinterpret_cast<uint32_t*>(dst + nb * 8) = pack_bf16x2(y0, y1);
+        }
+    }
+}
+
 }  // namespace
 
 cudaError_t hy_rmsnorm_pair(bool f32, const float* x, const int32_t* rows, const float* w1, void* out1, const float* w2, void* out2, int ldo, int T, int W, float eps, cudaStream_t s) {
@@ -194,6 +377,36 @@ cudaError_t hy_win_attention(bool f32, const HyWinAttn& a, const void* q, int ld
                               (float*)out, ldo, eps, r)
                : launch_plain(hy_win_attention_kernel<bf>, dim3(r.T, a.heads), dim3(128), smem, s, a, (const bf*)q, ldq, (const bf*)cache, sink, (const bf*)gate, ldg, (bf*)out, ldo,
                               eps, r);
+}
+
+bool hy_win_mma_supported(const HyWinAttn& a) {
+    const bool vd_ok = a.vdim == 16 || a.vdim == 32 || a.vdim == 64 || a.vdim == 96 || a.vdim == 128;
+    return hy_win_supported(a) && a.dim % 16 == 0 && a.dim <= 128 && vd_ok;
+}
+template <int MAPS, int NVB>
+static cudaError_t win_mma_launch(const HyWinAttn& a, const void* q, int ldq, const void* cache, const float* sink, const void* gate, int ldg, void* out, int ldo, float eps,
+                                  const HyRows& r, const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles, cudaStream_t s) {
+    using bf = __nv_bfloat16;
+    const int QP = MAPS * a.dim + 8, VP = NVB * 8 + 8;
+    const size_t smem = (size_t)(WIN_MQ * QP + 2 * WIN_KT * QP + 2 * WIN_KT * VP) * 2 + WIN_MQ * 4;
+    static size_t raised = 0;          // per instantiation
+    if (smem > 48 * 1024 && smem > raised) {
+        cudaError_t e = cudaFuncSetAttribute(hy_win_attention_mma_kernel<MAPS, NVB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        raised = smem;
+    }
+    return launch_plain(hy_win_attention_mma_kernel<MAPS, NVB>, dim3(n_tiles, a.kv_heads), dim3(128), smem, s, a, (const bf*)q, ldq, (const bf*)cache, sink, (const bf*)gate, ldg,
+                        (bf*)out, ldo, eps, r, tile_seq, tile_q0);
+}
+cudaError_t hy_win_attention_mma(const HyWinAttn& a, const void* q, int ldq, const void* cache, const float* sink, const void* gate, int ldg, void* out, int ldo, float eps,
+                                 const HyRows& r, const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles, cudaStream_t s) {
+    if (n_tiles <= 0) return cudaSuccess;
+    if (!hy_win_mma_supported(a)) return cudaErrorInvalidValue;
+#define WIN_CASE(M, N) if (a.maps == M && a.vdim == N * 8) return win_mma_launch<M, N>(a, q, ldq, cache, sink, gate, ldg, out, ldo, eps, r, tile_seq, tile_q0, n_tiles, s)
+    WIN_CASE(1, 2); WIN_CASE(1, 4); WIN_CASE(1, 8); WIN_CASE(1, 12); WIN_CASE(1, 16);
+    WIN_CASE(2, 2); WIN_CASE(2, 4); WIN_CASE(2, 8); WIN_CASE(2, 12); WIN_CASE(2, 16);
+#undef WIN_CASE
+    return cudaErrorInvalidValue;
 }
 
 }  // namespace oa
