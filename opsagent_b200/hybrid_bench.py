@@ -1,5 +1,6 @@
-"""Throughput of the Ratasun hybrid family beside the closest Llama-family model of equal width, depth and active feed-forward size
-(`bench.py --arch ratasun`).  Random weights (seeded on load), synthetic token ids; prefill = real chunked prefill of batch x (ctx-1) tokens,
+"""Throughput of the hybrid family beside the closest existing models (`bench.py --arch ratasun | zurevik`): Ratasun beside the Llama-family
+model of equal width, depth and active feed-forward size; Zurevik beside the Ratasun model of equal width, depth and experts (the closest
+design: the same parallel-residual layers with routed experts) and beside that Llama-family model.  Random weights (seeded on load), synthetic token ids; prefill = real chunked prefill of batch x (ctx-1) tokens,
 decode = steps of the whole batch, both timed with CUDA events inside the engine (oa_bench_decode).  With --breakdown the per-kernel-class
 device times come from the engine's in-situ event timing (OA_PROFILE_ALL), one pass for prefill and one for decode."""
 from __future__ import annotations
@@ -32,6 +33,22 @@ def sizes(name: str) -> dict:
     return {"hybrid": cfg, "llama": llama, "runs": runs}
 
 
+def zurevik_sizes(name: str) -> dict:
+    """Zurevik at the width, depth (6 layers), expert count and expert size of sizes(name): four differential layers (sliding window of 512 that keeps
+    the first 4 tokens) and two sink layers (window 1024), the second reading the first one's keys and values."""
+    if name == "small":
+        diff = {"heads": 16, "kv_heads": 4, "dim": 32, "vdim": 64, "diff": 0.4, "scale": 32 ** -0.5, "mask": {"size": 512, "keep_first": 4}}
+        sink = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 64, "scale": 64 ** -0.5, "mask": {"size": 1024}}
+        moe, width = {"kind": "moe", "expert": {"ff": 512}, "router": {"experts": 16, "top": 4}}, 1024
+    else:
+        diff = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 128, "diff": 0.4, "scale": 64 ** -0.5, "mask": {"size": 512, "keep_first": 4}}
+        sink = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024}}
+        moe, width = {"kind": "moe", "expert": {"ff": 1024}, "router": {"experts": 32, "top": 4}}, 2048
+    order = [("attention", diff), ("attention", diff), ("attention_2", sink), ("attention", diff), ("attention", diff), ("attention_2", dict(sink, kv_from=2))]
+    return {"architecture": "Zurevik", "width": width, "vocab": 32000, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "logit_softcap": 30.0,
+            "layers": [{"type": t, "mixer": m, "mlp": moe} for t, m in order]}
+
+
 def one(engine_cfg: dict, batch: int, ctx: int, steps: int, warmup: int, breakdown: bool) -> dict:
     from .engine import Engine
     out = {}
@@ -57,17 +74,27 @@ def one(engine_cfg: dict, batch: int, ctx: int, steps: int, warmup: int, breakdo
 
 
 def run(args) -> None:
-    res = {"metric": "hybrid_vs_llama_throughput", "unit": "tokens/s", "data": "synthetic", "dtype": "bf16", "cases": []}
+    zu = args.arch == "zurevik"
+    res = {"metric": "zurevik_vs_ratasun_and_llama_throughput" if zu else "hybrid_vs_llama_throughput", "unit": "tokens/s", "data": "synthetic", "dtype": "bf16", "cases": []}
     for name in args.arch_sizes.split(","):
         sz = sizes(name)
         batch, ctx = args.arch_batch, args.arch_ctx
         pages = batch * ((ctx + args.steps + args.warmup + 64) // 64 + 1)
         common = {"num_pages": pages, "max_batch": batch, "max_seq_len": (ctx + args.steps + args.warmup + 127) // 64 * 64, "max_step_tokens": 8192, "prefix_cache": 0}
-        with tempfile.TemporaryDirectory() as d:
-            with open(os.path.join(d, "config.json"), "w") as f:
-                json.dump(sz["hybrid"], f)
-            hy = one(dict(common, model_dir=d, **json.loads(args.engine_extra)), batch, ctx, args.steps, args.warmup, args.breakdown)
-        ll = one(dict(common, **sz["llama"]), batch, ctx, args.steps, args.warmup, args.breakdown)
-        res["cases"].append({"size": name, "batch": batch, "ctx": ctx, "layer_runs": sz["runs"], "ratasun": hy, "llama_equal_size": ll,
-                             "prefill_ratio": hy["prefill_tok_s"] / ll["prefill_tok_s"], "decode_ratio": hy["decode_tok_s"] / ll["decode_tok_s"]})
+
+        def folder_model(cfg):
+            with tempfile.TemporaryDirectory() as d:
+                with open(os.path.join(d, "config.json"), "w") as f:
+                    json.dump(cfg, f)
+                return one(dict(common, model_dir=d, **json.loads(args.engine_extra)), batch, ctx, args.steps, args.warmup, args.breakdown)
+        case = {"size": name, "batch": batch, "ctx": ctx, "layer_runs": sz["runs"]}
+        if zu:
+            case["zurevik"] = folder_model(zurevik_sizes(name))
+        case["ratasun"] = hy = folder_model(sz["hybrid"])
+        case["llama_equal_size"] = ll = one(dict(common, **sz["llama"]), batch, ctx, args.steps, args.warmup, args.breakdown)
+        new = case["zurevik"] if zu else hy
+        case["prefill_ratio"], case["decode_ratio"] = new["prefill_tok_s"] / ll["prefill_tok_s"], new["decode_tok_s"] / ll["decode_tok_s"]
+        if zu:
+            case["prefill_ratio_to_ratasun"], case["decode_ratio_to_ratasun"] = new["prefill_tok_s"] / hy["prefill_tok_s"], new["decode_tok_s"] / hy["decode_tok_s"]
+        res["cases"].append(case)
     print(json.dumps(res))
