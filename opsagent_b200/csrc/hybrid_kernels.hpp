@@ -62,6 +62,12 @@ bool hy_win_mma_supported(const HyWinAttn& a);
 cudaError_t hy_win_attention_mma(const HyWinAttn& a, const void* q, int ldq, const void* cache, const float* sink, const void* gate, int ldg, void* out, int ldo, float eps,
                                  const HyRows& r, const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles, cudaStream_t s);
 
+// decoding form of the same: tiles of at most HY_WIN_DECODE_QUERIES pairs (a decoding row's group of heads, a very short portion); the CTA's
+// warps deal the key tiles out among themselves and join their partial softmaxes in shared memory
+constexpr int HY_WIN_DECODE_QUERIES = 16;
+cudaError_t hy_win_decode_mma(const HyWinAttn& a, const void* q, int ldq, const void* cache, const float* sink, const void* gate, int ldg, void* out, int ldo, float eps,
+                              const HyRows& r, const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles, cudaStream_t s);
+
 struct HyLatentAttn {             // sizes of one latent-attention layer
     int heads, dim, rot_dim, vdim, kv_rank, rot_dims; float scale;
 };

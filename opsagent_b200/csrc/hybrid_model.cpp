@@ -344,7 +344,7 @@ HybridModel::HybridModel(const ModelConfig& c, const EngineOptions& o) : ModelBa
     for (const HyLayer& l : hc_.layers) if (l.type == HY_LATENT_ATTENTION) meta_cap_words_ += 3 * ((MR / 64 + (size_t)opt.max_batch) * l.heads + 8) + (size_t)opt.max_batch + 8;
     split_slots_ = std::min(16 * opt.max_batch, 4096);
     for (const HyLayer& l : hc_.layers) if (l.type == HY_LATENT_ATTENTION) meta_cap_words_ += 5 * (MR * l.heads / HY_MLA_TILE_QUERIES + (size_t)opt.max_batch + (size_t)split_slots_ + 8) + 3 * ((size_t)opt.max_batch + 4);
-    for (const HyLayer& l : hc_.layers) if (l.type == HY_WINDOW_ATTENTION) meta_cap_words_ += 2 * (MR * (size_t)(l.heads / l.kv_heads) / HY_WIN_TILE_QUERIES + (size_t)opt.max_batch + 8);
+    for (const HyLayer& l : hc_.layers) if (l.type == HY_WINDOW_ATTENTION) meta_cap_words_ += 2 * (MR * (size_t)(l.heads / l.kv_heads) / HY_WIN_TILE_QUERIES + 2 * (size_t)opt.max_batch + 16);
     if (hc_.n_caches > 0 && !f32_) { split_o_ = (float*)dmalloc((size_t)split_slots_ * max_lat * 4); split_ml_ = (float*)dmalloc((size_t)split_slots_ * max_lat_heads * 2 * 4); }
     for (int i = 0; i < 2; ++i) {
         cuda_check(cudaMallocHost(&h_meta_buf_[i], meta_cap_words_ * 4), "cudaMallocHost meta");
@@ -458,7 +458,7 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
     // tiles of 64 consecutive (row, head) pairs of one sequence, a decoding row with a long context cut into parts.
     struct TileList { bool mma = false, any_small = false; size_t o_seq = 0, o_q0 = 0, o_k0 = 0, o_k1 = 0, o_slot = 0, o_mrow = 0, o_mslot = 0, o_mparts = 0; int n = 0, n_merge = 0;
                       size_t o_pseq = 0, o_phead = 0, o_prow0 = 0, o_base = 0; int n_ptiles = 0, ctx_rows = 0, max_ctx = 0;
-                      size_t o_wseq = 0, o_wq0 = 0; int n_w = 0; };
+                      size_t o_wseq = 0, o_wq0 = 0, o_dseq = 0, o_dq0 = 0; int n_w = 0, n_d = 0; };
     std::vector<TileList> tile_lists(hc_.layers.size());
     for (size_t li = 0; li < hc_.layers.size(); ++li) {
         const HyLayer& l = hc_.layers[li]; TileList& tl = tile_lists[li];
@@ -467,11 +467,15 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
             tl.mma = !f32_ && opt.hy_tensor_core && ld_proj_ % 8 == 0 && ld_mix_ % 8 == 0 &&
                      hy_win_mma_supported(HyWinAttn{l.heads, l.kv_heads, l.dim, l.vdim, l.maps, l.window, l.keep_first, l.qk_norm, l.gate, l.scale, 0.f, 1.f});
             if (!tl.mma) continue;
-            tile_seq_.clear(); tile_q0_.clear();
+            tile_seq_.clear(); tile_q0_.clear(); ptile_seq_.clear(); ptile_row0_.clear();
             const int group = l.heads / l.kv_heads;
-            for (int sq = 0; sq < S; ++sq)
-                for (int q0 = 0, nq = (in.seq_row0[sq + 1] - in.seq_row0[sq]) * group; q0 < nq; q0 += HY_WIN_TILE_QUERIES) { tile_seq_.push_back(sq); tile_q0_.push_back(q0); }
+            for (int sq = 0; sq < S; ++sq) {
+                const int nq = (in.seq_row0[sq + 1] - in.seq_row0[sq]) * group;
+                if (nq <= HY_WIN_DECODE_QUERIES) { ptile_seq_.push_back(sq); ptile_row0_.push_back(0); continue; }       // decoding rows: the form whose warps split the keys
+                for (int q0 = 0; q0 < nq; q0 += HY_WIN_TILE_QUERIES) { tile_seq_.push_back(sq); tile_q0_.push_back(q0); }
+            }
             tl.n_w = (int)tile_seq_.size(); tl.o_wseq = put(tile_seq_.data(), tile_seq_.size()); tl.o_wq0 = put(tile_q0_.data(), tile_q0_.size());
+            tl.n_d = (int)ptile_seq_.size(); tl.o_dseq = put(ptile_seq_.data(), ptile_seq_.size()); tl.o_dq0 = put(ptile_row0_.data(), ptile_row0_.size());
             continue;
         }
         if (l.type != HY_LATENT_ATTENTION) continue;
@@ -546,9 +550,12 @@ void HybridModel::forward(const StepInput& in, float* logits_out) {
             cuda_check(hy_win_prep(f32_, a, at(proj_, w.off_a), ld_proj_, own ? at(proj_, w.off_b) : nullptr, own ? at(proj_, w.off_c) : nullptr, ld_proj_, w.q_norm, w.k_norm, hc_.eps,
                                    caches_[run.cache_idx], r, stream), "query / key norm + cache write"); MARK(23);
             const TileList& tl = tile_lists[run.layer];
-            if (tl.mma) cuda_check(hy_win_attention_mma(a, at(proj_, w.off_a), ld_proj_, caches_[run.cache_idx], w.sink, l.gate ? at(proj_, w.off_d) : nullptr, ld_proj_, mix_, ld_mix_,
-                                                        hc_.eps, r, d_meta_ + tl.o_wseq, d_meta_ + tl.o_wq0, tl.n_w, stream), "windowed attention (mma)");
-            else cuda_check(hy_win_attention(f32_, a, at(proj_, w.off_a), ld_proj_, caches_[run.cache_idx], w.sink, l.gate ? at(proj_, w.off_d) : nullptr, ld_proj_, mix_, ld_mix_, hc_.eps,
+            if (tl.mma) {
+                cuda_check(hy_win_attention_mma(a, at(proj_, w.off_a), ld_proj_, caches_[run.cache_idx], w.sink, l.gate ? at(proj_, w.off_d) : nullptr, ld_proj_, mix_, ld_mix_,
+                                                hc_.eps, r, d_meta_ + tl.o_wseq, d_meta_ + tl.o_wq0, tl.n_w, stream), "windowed attention (mma)");
+                cuda_check(hy_win_decode_mma(a, at(proj_, w.off_a), ld_proj_, caches_[run.cache_idx], w.sink, l.gate ? at(proj_, w.off_d) : nullptr, ld_proj_, mix_, ld_mix_,
+                                             hc_.eps, r, d_meta_ + tl.o_dseq, d_meta_ + tl.o_dq0, tl.n_d, stream), "windowed attention (mma, decoding rows)");
+            } else cuda_check(hy_win_attention(f32_, a, at(proj_, w.off_a), ld_proj_, caches_[run.cache_idx], w.sink, l.gate ? at(proj_, w.off_d) : nullptr, ld_proj_, mix_, ld_mix_, hc_.eps,
                                              r, stream), "windowed attention");
             MARK(24);
         } else if (l.type == HY_LATENT_ATTENTION) {

@@ -341,6 +341,197 @@ __global__ void __launch_bounds__(128) hy_win_attention_mma_kernel(HyWinAttn a, 
     }
 }
 
+// Decoding form of the same computation, for tiles of at most 16 query slots (a decoding row's group of heads, or a very short portion): the
+// prefill form above would leave three of its four warps idle and walk the window tile by tile on one warp.  Here the CTA's eight warps
+// deal the visible key tiles out among themselves (warp w takes tiles w, w + 8, ...), each with its own shared-memory tile and its own
+// online softmax over the same 16 query slots; the partial sums, maxima and denominators then meet in shared memory and 16 threads per
+// query slot join them in warp order and finish the head (sink, a1 - lambda a2, unit RMS, gate).  Which tiles a warp takes depends on the
+// row's position only.
+constexpr int WIN_DEC_WARPS = 8;
+template <int MAPS, int NVB>
+__global__ void __launch_bounds__(256) hy_win_decode_mma_kernel(HyWinAttn a, const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ cache,
+                                                                const float* __restrict__ sink, const __nv_bfloat16* __restrict__ gate, int ldg,
+                                                                __nv_bfloat16* __restrict__ out, int ldo, float eps, HyRows r, const int32_t* __restrict__ tile_seq,
+                                                                const int32_t* __restrict__ tile_q0) {
+    HY_PDL();
+    extern __shared__ __align__(16) uint8_t win_smem[];
+    __shared__ float pm[WIN_DEC_WARPS][MAPS][16], pl[WIN_DEC_WARPS][MAPS][16];
+    __shared__ int qpos[16];
+    constexpr int VD = NVB * 8, VP = VD + 8;
+    const int D = a.dim, QD = MAPS * D, QP = QD + 8, HG = a.heads / a.kv_heads, g = blockIdx.y;
+    const int KW = a.kv_heads * QD, CW = KW + a.kv_heads * VD;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(win_smem);      // [16][QP]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    __nv_bfloat16* Kw = Qs + 16 * QP + (size_t)warp * WIN_KT * (QP + VP);     // this warp's tile: [32][QP] keys, [32][VP] values
+    __nv_bfloat16* Vw = Kw + WIN_KT * QP;
+    float* po = reinterpret_cast<float*>(Qs + 16 * QP);                  // after the loop: [warps][MAPS][16][VD] partial sums over the tile buffers
+    const int seq = tile_seq[blockIdx.x], q0 = tile_q0[blockIdx.x];
+    const int row0 = r.seq_row0[seq], len = r.seq_row0[seq + 1] - row0;
+    const int nq = min(16, len * HG - q0);
+    for (int idx = tid; idx < 16 * (QD / 8); idx += 256) {
+        const int qi = idx / (QD / 8), c = idx - qi * (QD / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (qi < nq) v = *reinterpret_cast<const uint4*>(q + (long long)(row0 + (q0 + qi) / HG) * ldq + (long long)(g * HG + (q0 + qi) % HG) * QD + c * 8);
+        *reinterpret_cast<uint4*>(Qs + qi * QP + c * 8) = v;
+    }
+    if (tid < 16) qpos[tid] = tid < nq ? r.positions[row0 + (q0 + tid) / HG] : -1;
+    __syncthreads();
+    const int pos_min = r.positions[row0 + q0 / HG], pos_max = r.positions[row0 + (q0 + nq - 1) / HG];
+    const int lo_min = max(0, pos_min - a.window + 1);
+    const int win_t0 = lo_min / WIN_KT, n_kt = pos_max / WIN_KT + 1;
+    const int n_keep = min((min(a.keep_first, lo_min) + WIN_KT - 1) / WIN_KT, win_t0);
+    const int n_it = n_keep + (n_kt - win_t0);
+    const int32_t* bt = r.block_tables + (long long)seq * r.max_pages_per_seq;
+    float o[MAPS][NVB][4];
+    float m_lo[MAPS], m_hi[MAPS], l_lo[MAPS], l_hi[MAPS];
+#pragma unroll
+    for (int mp = 0; mp < MAPS; ++mp) {
+        m_lo[mp] = m_hi[mp] = -INFINITY; l_lo[mp] = l_hi[mp] = 0.f;
+#pragma unroll
+        for (int i = 0; i < NVB; ++i) { o[mp][i][0] = o[mp][i][1] = o[mp][i][2] = o[mp][i][3] = 0.f; }
+    }
+    const float qscale = a.scale * 1.4426950408889634f;
+    const int p_lo = qpos[lane >> 2], p_hi = qpos[(lane >> 2) + 8];
+    for (int it = warp; it < n_it; it += WIN_DEC_WARPS) {
+        const int kt = it < n_keep ? it : win_t0 + (it - n_keep);
+        __syncwarp();                                  // the previous tile has been read by every lane
+        {
+            const int kc = QD / 8, vc = VD / 8;
+            for (int idx = lane; idx < WIN_KT * (kc + vc); idx += 32) {
+                const int j = idx / (kc + vc), c = idx - j * (kc + vc), key = kt * WIN_KT + j;
+                __nv_bfloat16* dst = c < kc ? Kw + j * QP + c * 8 : Vw + j * VP + (c - kc) * 8;
+                if (key <= pos_max) {
+                    const __nv_bfloat16* row = cache + ((long long)bt[key >> 6] * 64 + (key & 63)) * CW;
+                    cp_async16(dst, c < kc ? row + (long long)g * QD + c * 8 : row + KW + (long long)g * VD + (c - kc) * 8);
+                } else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncwarp();
+        uint32_t pa[MAPS][2][4];
+#pragma unroll
+        for (int mp = 0; mp < MAPS; ++mp) {
+            float s[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+            const uint32_t qa = smem_u32(Qs + (lane & 15) * QP + mp * D + (lane >> 4) * 8);
+            const uint32_t ka = smem_u32(Kw + ((lane >> 4) * 8 + (lane & 7)) * QP + mp * D + ((lane >> 3) & 1) * 8);
+            for (int ks = 0; ks < D / 16; ++ks) {
+                uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                ldmatrix_x4(qa + ks * 32, a0, a1, a2, a3);
+                ldmatrix_x4(ka + ks * 32, b0, b1, b2, b3);
+                mma_bf16_16816(s[0], a0, a1, a2, a3, b0, b1); mma_bf16_16816(s[1], a0, a1, a2, a3, b2, b3);
+                ldmatrix_x4(ka + 16 * QP * 2 + ks * 32, b0, b1, b2, b3);
+                mma_bf16_16816(s[2], a0, a1, a2, a3, b0, b1); mma_bf16_16816(s[3], a0, a1, a2, a3, b2, b3);
+            }
+            float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+            for (int nb = 0; nb < 4; ++nb)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int key = kt * WIN_KT + nb * 8 + (lane & 3) * 2 + (c & 1), p = c < 2 ? p_lo : p_hi;
+                    const bool vis = key <= p && (p - key < a.window || key < a.keep_first);
+                    s[nb][c] = vis ? s[nb][c] * qscale : -INFINITY;
+                    if (c < 2) mx_lo = fmaxf(mx_lo, s[nb][c]); else mx_hi = fmaxf(mx_hi, s[nb][c]);
+                }
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1)); mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)); mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+            const float n_lo = fmaxf(m_lo[mp], mx_lo), n_hi = fmaxf(m_hi[mp], mx_hi);
+            const float b_lo = n_lo == -INFINITY ? 0.f : n_lo, b_hi = n_hi == -INFINITY ? 0.f : n_hi;
+            const float c_lo = exp2f(m_lo[mp] - b_lo), c_hi = exp2f(m_hi[mp] - b_hi);
+            m_lo[mp] = n_lo; m_hi[mp] = n_hi;
+            float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+            for (int nb = 0; nb < 4; ++nb) {
+                s[nb][0] = exp2f(s[nb][0] - b_lo); s[nb][1] = exp2f(s[nb][1] - b_lo); s[nb][2] = exp2f(s[nb][2] - b_hi); s[nb][3] = exp2f(s[nb][3] - b_hi);
+                sum_lo += s[nb][0] + s[nb][1]; sum_hi += s[nb][2] + s[nb][3];
+            }
+            l_lo[mp] = l_lo[mp] * c_lo + sum_lo; l_hi[mp] = l_hi[mp] * c_hi + sum_hi;
+#pragma unroll
+            for (int i = 0; i < NVB; ++i) { o[mp][i][0] *= c_lo; o[mp][i][1] *= c_lo; o[mp][i][2] *= c_hi; o[mp][i][3] *= c_hi; }
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+                pa[mp][kk][0] = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]); pa[mp][kk][1] = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
+                pa[mp][kk][2] = pack_bf16x2(s[2 * kk + 1][0], s[2 * kk + 1][1]); pa[mp][kk][3] = pack_bf16x2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+            }
+        }
+        const uint32_t va = smem_u32(Vw + (((lane >> 3) & 1) * 8 + (lane & 7)) * VP + (lane >> 4) * 8);
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk)
+#pragma unroll
+            for (int np = 0; np < NVB / 2; ++np) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(va + kk * 16 * VP * 2 + np * 32, b0, b1, b2, b3);
+#pragma unroll
+                for (int mp = 0; mp < MAPS; ++mp) {
+                    mma_bf16_16816(o[mp][2 * np], pa[mp][kk][0], pa[mp][kk][1], pa[mp][kk][2], pa[mp][kk][3], b0, b1);
+                    mma_bf16_16816(o[mp][2 * np + 1], pa[mp][kk][0], pa[mp][kk][1], pa[mp][kk][2], pa[mp][kk][3], b2, b3);
+                }
+            }
+    }
+    __syncthreads();                                   // every warp is done with its tile buffer: the partials go over them
+#pragma unroll
+    for (int mp = 0; mp < MAPS; ++mp) {
+        float ll = l_lo[mp], lh = l_hi[mp];
+        ll += __shfl_xor_sync(0xffffffffu, ll, 1); ll += __shfl_xor_sync(0xffffffffu, ll, 2);
+        lh += __shfl_xor_sync(0xffffffffu, lh, 1); lh += __shfl_xor_sync(0xffffffffu, lh, 2);
+        if ((lane & 3) == 0) { pm[warp][mp][lane >> 2] = m_lo[mp]; pm[warp][mp][(lane >> 2) + 8] = m_hi[mp]; pl[warp][mp][lane >> 2] = ll; pl[warp][mp][(lane >> 2) + 8] = lh; }
+        float* dst = po + ((size_t)(warp * MAPS + mp) * 16 + (lane >> 2)) * VD + (lane & 3) * 2;
+#pragma unroll
+        for (int nb = 0; nb < NVB; ++nb) {
+            *reinterpret_cast<float2*>(dst + nb * 8) = make_float2(o[mp][nb][0], o[mp][nb][1]);
+            *reinterpret_cast<float2*>(dst + 8 * VD + nb * 8) = make_float2(o[mp][nb][2], o[mp][nb][3]);
+        }
+    }
+    __syncthreads();
+    // 16 threads per query slot: channels sub, sub + 16, ...
+    const int qi = tid >> 4, sub = tid & 15;
+    const bool ok = qi < nq;
+    const int row = row0 + (q0 + (ok ? qi : 0)) / HG, head = g * HG + (q0 + (ok ? qi : 0)) % HG;
+    float wgt[MAPS][WIN_DEC_WARPS], inv[MAPS];
+#pragma unroll
+    for (int mp = 0; mp < MAPS; ++mp) {
+        float M = sink ? sink[head] * 1.4426950408889634f : -INFINITY, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < WIN_DEC_WARPS; ++w) M = fmaxf(M, pm[w][mp][qi]);
+#pragma unroll
+        for (int w = 0; w < WIN_DEC_WARPS; ++w) { wgt[mp][w] = pm[w][mp][qi] == -INFINITY ? 0.f : exp2f(pm[w][mp][qi] - M); L = fmaf(wgt[mp][w], pl[w][mp][qi], L); }
+        if (sink) L += exp2f(sink[head] * 1.4426950408889634f - M);
+        inv[mp] = L > 0.f ? 1.0f / L : 0.f;
+    }
+    float y[NVB / 2], ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NVB / 2; ++i) {
+        const int c = sub + 16 * i;
+        float v[MAPS];
+#pragma unroll
+        for (int mp = 0; mp < MAPS; ++mp) {
+            float acc = 0.f;
+#pragma unroll
+            for (int w = 0; w < WIN_DEC_WARPS; ++w) acc = fmaf(wgt[mp][w], po[((size_t)(w * MAPS + mp) * 16 + qi) * VD + c], acc);
+            v[mp] = acc * inv[mp];
+        }
+        y[i] = MAPS == 2 ? v[0] - a.lambda * v[MAPS - 1] : v[0];
+        ss = fmaf(y[i], y[i], ss);
+    }
+    float post = 1.f;
+    if (MAPS == 2) {
+#pragma unroll
+        for (int sh = 1; sh < 16; sh <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, sh);
+        post = a.out_scale / sqrtf(ss / (float)VD + eps);
+    }
+    if (!ok) return;
+    if (a.gate == 2) post *= sigmoidf_(__bfloat162float(gate[(long long)row * ldg + head]));
+#pragma unroll
+    for (int i = 0; i < NVB / 2; ++i) {
+        const int c = sub + 16 * i;
+        float v = y[i] * post;
+        if (a.gate == 1) v *= sigmoidf_(__bfloat162float(gate[(long long)row * ldg + (long long)head * VD + c]));
+        out[(long long)row * ldo + (long long)head * VD + c] = __float2bfloat16_rn(v);
+    }
+}
+
 }  // namespace
 
 cudaError_t hy_rmsnorm_pair(bool f32, const float* x, const int32_t* rows, const float* w1, void* out1, const float* w2, void* out2, int ldo, int T, int W, float eps, cudaStream_t s) {
@@ -398,11 +589,37 @@ static cudaError_t win_mma_launch(const HyWinAttn& a, const void* q, int ldq, co
     return launch_plain(hy_win_attention_mma_kernel<MAPS, NVB>, dim3(n_tiles, a.kv_heads), dim3(128), smem, s, a, (const bf*)q, ldq, (const bf*)cache, sink, (const bf*)gate, ldg,
                         (bf*)out, ldo, eps, r, tile_seq, tile_q0);
 }
+template <int MAPS, int NVB>
+static cudaError_t win_decode_launch(const HyWinAttn& a, const void* q, int ldq, const void* cache, const float* sink, const void* gate, int ldg, void* out, int ldo, float eps,
+                                     const HyRows& r, const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles, cudaStream_t s) {
+    using bf = __nv_bfloat16;
+    const int QP = MAPS * a.dim + 8, VP = NVB * 8 + 8;
+    const size_t tiles = (size_t)WIN_DEC_WARPS * WIN_KT * (QP + VP) * 2, parts = (size_t)WIN_DEC_WARPS * MAPS * 16 * NVB * 8 * 4;
+    const size_t smem = (size_t)16 * QP * 2 + (tiles > parts ? tiles : parts);
+    static size_t raised = 0;
+    if (smem > 48 * 1024 && smem > raised) {
+        cudaError_t e = cudaFuncSetAttribute(hy_win_decode_mma_kernel<MAPS, NVB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        raised = smem;
+    }
+    return launch_plain(hy_win_decode_mma_kernel<MAPS, NVB>, dim3(n_tiles, a.kv_heads), dim3(256), smem, s, a, (const bf*)q, ldq, (const bf*)cache, sink, (const bf*)gate, ldg,
+                        (bf*)out, ldo, eps, r, tile_seq, tile_q0);
+}
 cudaError_t hy_win_attention_mma(const HyWinAttn& a, const void* q, int ldq, const void* cache, const float* sink, const void* gate, int ldg, void* out, int ldo, float eps,
                                  const HyRows& r, const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles, cudaStream_t s) {
     if (n_tiles <= 0) return cudaSuccess;
     if (!hy_win_mma_supported(a)) return cudaErrorInvalidValue;
 #define WIN_CASE(M, N) if (a.maps == M && a.vdim == N * 8) return win_mma_launch<M, N>(a, q, ldq, cache, sink, gate, ldg, out, ldo, eps, r, tile_seq, tile_q0, n_tiles, s)
+    WIN_CASE(1, 2); WIN_CASE(1, 4); WIN_CASE(1, 8); WIN_CASE(1, 12); WIN_CASE(1, 16);
+    WIN_CASE(2, 2); WIN_CASE(2, 4); WIN_CASE(2, 8); WIN_CASE(2, 12); WIN_CASE(2, 16);
+#undef WIN_CASE
+    return cudaErrorInvalidValue;
+}
+cudaError_t hy_win_decode_mma(const HyWinAttn& a, const void* q, int ldq, const void* cache, const float* sink, const void* gate, int ldg, void* out, int ldo, float eps,
+                              const HyRows& r, const int32_t* tile_seq, const int32_t* tile_q0, int n_tiles, cudaStream_t s) {
+    if (n_tiles <= 0) return cudaSuccess;
+    if (!hy_win_mma_supported(a)) return cudaErrorInvalidValue;
+#define WIN_CASE(M, N) if (a.maps == M && a.vdim == N * 8) return win_decode_launch<M, N>(a, q, ldq, cache, sink, gate, ldg, out, ldo, eps, r, tile_seq, tile_q0, n_tiles, s)
     WIN_CASE(1, 2); WIN_CASE(1, 4); WIN_CASE(1, 8); WIN_CASE(1, 12); WIN_CASE(1, 16);
     WIN_CASE(2, 2); WIN_CASE(2, 4); WIN_CASE(2, 8); WIN_CASE(2, 12); WIN_CASE(2, 16);
 #undef WIN_CASE
