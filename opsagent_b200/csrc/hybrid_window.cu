@@ -194,7 +194,8 @@ __global__ void __launch_bounds__(128) hy_win_attention_mma_kernel(HyWinAttn a, 
         *reinterpret_cast<uint4*>(Qs + qi * QP + c * 8) = v;
     }
     for (int qi = tid; qi < WIN_MQ; qi += 128) qpos[qi] = qi < nq ? r.positions[row0 + (q0 + qi) / HG] : -1;
-    const int pos_min = r.positions[row0 + q0 / HG], pos_max = r.positions[row0 + (q0 + nq - 1) / HG];
+    auto qpos_of = [&](int qi) { return r.positions[row0 + (q0 + qi) / HG]; };
+    const int pos_min = qpos_of(0), pos_max = qpos_of(nq - 1);
     const int lo_min = max(0, pos_min - a.window + 1);
     const int win_t0 = lo_min / WIN_KT, n_kt = pos_max / WIN_KT + 1;
     const int n_keep = min((min(a.keep_first, lo_min) + WIN_KT - 1) / WIN_KT, win_t0);      // tiles of kept first positions that lie wholly below the window's first tile
@@ -223,6 +224,7 @@ __global__ void __launch_bounds__(128) hy_win_attention_mma_kernel(HyWinAttn a, 
     }
     const float qscale = a.scale * 1.4426950408889634f;
     const bool active = 16 * warp < nq;
+    const int wp_min = active ? qpos_of(16 * warp) : 0, wp_max = active ? qpos_of(min(16 * warp + 15, nq - 1)) : 0;      // positions of the warp's first and last query slot
     load_tile(0, 0);
     for (int it = 0; it < n_it; ++it) {
         if (it + 1 < n_it) { load_tile(it + 1, (it + 1) & 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
@@ -232,6 +234,9 @@ __global__ void __launch_bounds__(128) hy_win_attention_mma_kernel(HyWinAttn a, 
             const int kt = it < n_keep ? it : win_t0 + (it - n_keep);
             const __nv_bfloat16* Kb = Ks + (it & 1) * WIN_KT * QP; const __nv_bfloat16* Vb = Vs + (it & 1) * WIN_KT * VP;
             const int p_lo = qpos[16 * warp + (lane >> 2)], p_hi = qpos[16 * warp + (lane >> 2) + 8];
+            // every key of the tile visible to every query slot of this warp (inside all of their windows, or all kept first positions): no mask
+            const int k_first = kt * WIN_KT, k_last = k_first + WIN_KT - 1;
+            const bool whole = k_last <= wp_min && (k_first > wp_max - a.window || k_last < a.keep_first);
             uint32_t pa[MAPS][2][4];        // P of this tile as A fragments, per map and 16-key half
 #pragma unroll
             for (int mp = 0; mp < MAPS; ++mp) {
@@ -249,31 +254,37 @@ __global__ void __launch_bounds__(128) hy_win_attention_mma_kernel(HyWinAttn a, 
                     mma_bf16_16816(s[2], a0, a1, a2, a3, b0, b1); mma_bf16_16816(s[3], a0, a1, a2, a3, b2, b3);
                 }
                 float mx_lo = -INFINITY, mx_hi = -INFINITY;
+                if (!whole) {                          // a tile on an edge of the mask: per query position
 #pragma unroll
-                for (int nb = 0; nb < 4; ++nb)
+                    for (int nb = 0; nb < 4; ++nb)
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const int key = kt * WIN_KT + nb * 8 + (lane & 3) * 2 + (c & 1), p = c < 2 ? p_lo : p_hi;
-                        const bool vis = key <= p && (p - key < a.window || key < a.keep_first);
-                        s[nb][c] = vis ? s[nb][c] * qscale : -INFINITY;
-                        if (c < 2) mx_lo = fmaxf(mx_lo, s[nb][c]); else mx_hi = fmaxf(mx_hi, s[nb][c]);
-                    }
+                        for (int c = 0; c < 4; ++c) {
+                            const int key = kt * WIN_KT + nb * 8 + (lane & 3) * 2 + (c & 1), p = c < 2 ? p_lo : p_hi;
+                            if (!(key <= p && (p - key < a.window || key < a.keep_first))) s[nb][c] = -INFINITY;
+                        }
+                }
+#pragma unroll
+                for (int nb = 0; nb < 4; ++nb) { mx_lo = fmaxf(mx_lo, fmaxf(s[nb][0], s[nb][1])); mx_hi = fmaxf(mx_hi, fmaxf(s[nb][2], s[nb][3])); }
                 mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1)); mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
                 mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)); mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-                // a tile may hold no visible key for some of its rows (their window starts later): the running maximum then stays -inf
-                const float n_lo = fmaxf(m_lo[mp], mx_lo), n_hi = fmaxf(m_hi[mp], mx_hi);
+                // the running maximum is kept in scaled base-2 units; the raw scores are scaled inside the exponent's multiply-add.  A tile may
+                // hold no visible key for some of its rows (their window starts later): their maximum then stays -inf
+                const float n_lo = fmaxf(m_lo[mp], mx_lo * qscale), n_hi = fmaxf(m_hi[mp], mx_hi * qscale);
                 const float b_lo = n_lo == -INFINITY ? 0.f : n_lo, b_hi = n_hi == -INFINITY ? 0.f : n_hi;
                 const float c_lo = exp2f(m_lo[mp] - b_lo), c_hi = exp2f(m_hi[mp] - b_hi);
                 m_lo[mp] = n_lo; m_hi[mp] = n_hi;
                 float sum_lo = 0.f, sum_hi = 0.f;
 #pragma unroll
                 for (int nb = 0; nb < 4; ++nb) {
-                    s[nb][0] = exp2f(s[nb][0] - b_lo); s[nb][1] = exp2f(s[nb][1] - b_lo); s[nb][2] = exp2f(s[nb][2] - b_hi); s[nb][3] = exp2f(s[nb][3] - b_hi);
+                    s[nb][0] = exp2f(fmaf(s[nb][0], qscale, -b_lo)); s[nb][1] = exp2f(fmaf(s[nb][1], qscale, -b_lo));
+                    s[nb][2] = exp2f(fmaf(s[nb][2], qscale, -b_hi)); s[nb][3] = exp2f(fmaf(s[nb][3], qscale, -b_hi));
                     sum_lo += s[nb][0] + s[nb][1]; sum_hi += s[nb][2] + s[nb][3];
                 }
                 l_lo[mp] = l_lo[mp] * c_lo + sum_lo; l_hi[mp] = l_hi[mp] * c_hi + sum_hi;
+                if (__any_sync(0xffffffffu, c_lo != 1.f || c_hi != 1.f)) {      // no row's maximum rose: the sums keep their scale
 #pragma unroll
-                for (int i = 0; i < NVB; ++i) { o[mp][i][0] *= c_lo; o[mp][i][1] *= c_lo; o[mp][i][2] *= c_hi; o[mp][i][3] *= c_hi; }
+                    for (int i = 0; i < NVB; ++i) { o[mp][i][0] *= c_lo; o[mp][i][1] *= c_lo; o[mp][i][2] *= c_hi; o[mp][i][3] *= c_hi; }
+                }
 #pragma unroll
                 for (int kk = 0; kk < 2; ++kk) {
                     pa[mp][kk][0] = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]); pa[mp][kk][1] = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
