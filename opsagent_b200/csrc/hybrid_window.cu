@@ -57,6 +57,42 @@ __global__ void __launch_bounds__(128) hy_win_prep_kernel(HyWinAttn a, TA* __res
     if (v) for (int c = threadIdx.x; c < a.kv_heads * a.vdim; c += blockDim.x) crow[KW + c] = v[(long long)t * ldkv + c];
 }
 
+// The same for bf16 rows whose vectors come in aligned groups of 8 channels and whose dim / 8 is a power of two up to 32: a lane owns 16 bytes of a
+// vector, the dim / 8 lanes of a vector meet by shuffles, every access is 16 bytes wide.  Sums run per lane and then over lanes, so the
+// rounding of the norm differs from the kernel above in the last fp32 bit only; a model takes one of the two for all of its steps.
+__global__ void __launch_bounds__(128) hy_win_prep_vec8_kernel(HyWinAttn a, __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ k,
+                                                               const __nv_bfloat16* __restrict__ v, int ldkv, const float* __restrict__ qw, const float* __restrict__ kw, float eps,
+                                                               __nv_bfloat16* __restrict__ cache, HyRows r) {
+    HY_PDL();
+    const int t = blockIdx.x, tid = threadIdx.x, D = a.dim, GS = D / 8;
+    const int nq = a.qk_norm ? a.heads * a.maps : 0, nk = k ? a.kv_heads * a.maps : 0, KW = a.kv_heads * a.maps * D, CW = KW + a.kv_heads * a.vdim;
+    __nv_bfloat16* crow = cache + (long long)r.slots[t] * CW;
+    const int per_pass = 128 / GS, part = tid % GS;
+    for (int base = 0; base < nq + nk; base += per_pass) {
+        const int u = base + tid / GS; const bool ok = u < nq + nk, is_q = u < nq; const int i = is_q ? u : u - nq;
+        const __nv_bfloat16* src = is_q ? q + (long long)t * ldq + (long long)i * D + part * 8 : k + (long long)t * ldkv + (long long)i * D + part * 8;
+        __nv_bfloat16* dst = is_q ? q + (long long)t * ldq + (long long)i * D + part * 8 : crow + (long long)i * D + part * 8;
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (ok) raw = *reinterpret_cast<const uint4*>(src);
+        if (a.qk_norm) {
+            const float x[8] = {bf16lo(raw.x), bf16hi(raw.x), bf16lo(raw.y), bf16hi(raw.y), bf16lo(raw.z), bf16hi(raw.z), bf16lo(raw.w), bf16hi(raw.w)};
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
+            for (int o = 1; o < GS; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float rr = 1.0f / sqrtf(ss / (float)D + eps);
+            if (ok) {
+                const float* w = (is_q ? qw : kw) + part * 8;
+                const float4 w0 = *reinterpret_cast<const float4*>(w), w1 = *reinterpret_cast<const float4*>(w + 4);
+                raw.x = pack_bf16x2(x[0] * rr * w0.x, x[1] * rr * w0.y); raw.y = pack_bf16x2(x[2] * rr * w0.z, x[3] * rr * w0.w);
+                raw.z = pack_bf16x2(x[4] * rr * w1.x, x[5] * rr * w1.y); raw.w = pack_bf16x2(x[6] * rr * w1.z, x[7] * rr * w1.w);
+            }
+        }
+        if (ok) *reinterpret_cast<uint4*>(dst) = raw;
+    }
+    if (v) for (int c = tid * 8; c < a.kv_heads * a.vdim; c += 128 * 8) *reinterpret_cast<uint4*>(crow + KW + c) = *reinterpret_cast<const uint4*>(v + (long long)t * ldkv + c);
+}
+
 // The visible keys of a query at position p, in the order every kernel walks them: the kept first positions that the window no longer
 // covers, then the window.  n = count; key(i) = i-th visible position.
 struct WinKeys {
@@ -555,6 +591,11 @@ cudaError_t hy_win_prep(bool f32, const HyWinAttn& a, void* q, int ldq, const vo
                         const HyRows& r, cudaStream_t s) {
     if (r.T <= 0 || (!a.qk_norm && !k)) return cudaSuccess;
     using bf = __nv_bfloat16;
+    const int gs = a.dim / 8;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(cache) |
+                           reinterpret_cast<uintptr_t>(q_norm_w) | reinterpret_cast<uintptr_t>(k_norm_w)) & 15) == 0;
+    if (!f32 && a.dim % 8 == 0 && gs <= 32 && (gs & (gs - 1)) == 0 && a.vdim % 8 == 0 && ldq % 8 == 0 && ldkv % 8 == 0 && aligned)
+        return launch_plain(hy_win_prep_vec8_kernel, dim3(r.T), dim3(128), 0, s, a, (bf*)q, ldq, (const bf*)k, (const bf*)v, ldkv, q_norm_w, k_norm_w, eps, (bf*)cache, r);
     return f32 ? launch_plain(hy_win_prep_kernel<float>, dim3(r.T), dim3(128), 0, s, a, (float*)q, ldq, (const float*)k, (const float*)v, ldkv, q_norm_w, k_norm_w, eps, (float*)cache, r)
                : launch_plain(hy_win_prep_kernel<bf>, dim3(r.T), dim3(128), 0, s, a, (bf*)q, ldq, (const bf*)k, (const bf*)v, ldkv, q_norm_w, k_norm_w, eps, (bf*)cache, r);
 }
