@@ -35,17 +35,17 @@ def sizes(name: str) -> dict:
 
 def zurevik_sizes(name: str) -> dict:
     """Zurevik at the width, depth (6 layers), expert count and expert size of sizes(name): four differential layers (sliding window of 512 that keeps
-    the first 4 tokens) and two sink layers (window 1024), the second reading the first one's keys and values."""
+    the first 8 tokens) and two sink layers (window 1024), the second reading the first one's keys and values."""
     if name == "small":
-        diff = {"heads": 16, "kv_heads": 4, "dim": 32, "vdim": 64, "diff": 0.4, "scale": 32 ** -0.5, "mask": {"size": 512, "keep_first": 4}}
+        diff = {"heads": 16, "kv_heads": 4, "dim": 32, "vdim": 64, "diff": 0.4, "scale": 32 ** -0.5, "mask": {"size": 512, "keep_first": 8}}
         sink = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 64, "scale": 64 ** -0.5, "mask": {"size": 1024}}
         moe, width = {"kind": "moe", "expert": {"ff": 512}, "router": {"experts": 16, "top": 4}}, 1024
     else:
-        diff = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 128, "diff": 0.4, "scale": 64 ** -0.5, "mask": {"size": 512, "keep_first": 4}}
+        diff = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 128, "diff": 0.4, "scale": 64 ** -0.5, "mask": {"size": 512, "keep_first": 8}}
         sink = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024}}
         moe, width = {"kind": "moe", "expert": {"ff": 1024}, "router": {"experts": 32, "top": 4}}, 2048
     order = [("attention", diff), ("attention", diff), ("attention_2", sink), ("attention", diff), ("attention", diff), ("attention_2", dict(sink, kv_from=2))]
-    return {"architecture": "Zurevik", "width": width, "vocab": 32000, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "logit_softcap": 30.0,
+    return {"architecture": "Zurevik", "width": width, "vocab": 32000, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "logit_softcap": 50.0,
             "layers": [{"type": t, "mixer": m, "mlp": moe} for t, m in order]}
 
 

@@ -199,13 +199,26 @@ def test_long_decoding(tmp_path):
         check(replay(eng, 1, toks, [3]), Z.forward(cfg, W, toks), "float32")     # 197 single-token steps over three page borders, every window passed
 
 
-def test_bf16_tensor_core_path_and_plain_path_agree_with_the_oracle(tmp_path):
-    """Head sizes that take the tensor-core attention kernels (multiples of 16) in prompts long enough for several query and key tiles,
-    with windows that cut tiles, beside the plain kernels (hy_tensor_core = 0)."""
-    layers = [Z.diff_layer(heads=4, kv_heads=2, dim=32, vdim=48, window=75, keep_first=5, diff=0.45, mlp=MOE),
-              Z.sink_layer(heads=4, kv_heads=1, dim=48, vdim=32, window=141, mlp=Z.moe(experts=8, top=2, ff=64)),
-              Z.diff_layer(heads=2, kv_heads=2, dim=16, vdim=16, window=200, keep_first=70, diff=0.25), Z.sink_layer(heads=2, kv_heads=1, dim=48, vdim=32, window=40, kv_from=1)]
-    cfg = Z.make_config(layers, width=64, vocab=96)
+TC_STACKS = {
+    # head sizes that take the tensor-core attention kernels (dim a multiple of 16, vdim 16 / 32 / 64 / 96 / 128), windows that cut tiles
+    "three_k_steps_and_96_value_channels": [Z.diff_layer(heads=4, kv_heads=2, dim=32, vdim=96, window=75, keep_first=5, diff=0.45, mlp=MOE),
+                                            Z.sink_layer(heads=4, kv_heads=1, dim=48, vdim=32, window=141, mlp=Z.moe(experts=8, top=2, ff=64)),
+                                            Z.diff_layer(heads=2, kv_heads=2, dim=16, vdim=16, window=200, keep_first=70, diff=0.25),
+                                            Z.sink_layer(heads=2, kv_heads=1, dim=48, vdim=32, window=40, kv_from=1)],
+    # the widest tiles (two maps x 128 value channels), a group of 8 heads per key/value head, and a group of 20: more query slots per decoding
+    # row than the decoding form takes, so its rows go through the 64-slot form (no experts here: no choice can flip, the worst row stays sharp)
+    "widest_tiles_and_large_groups": [Z.diff_layer(heads=2, kv_heads=1, dim=64, vdim=128, window=90, keep_first=33, diff=0.35),
+                                      Z.sink_layer(heads=8, kv_heads=1, dim=128, vdim=64, window=65),
+                                      Z.sink_layer(heads=40, kv_heads=2, dim=16, vdim=16, window=100),
+                                      Z.diff_layer(heads=6, kv_heads=2, dim=16, vdim=64, window=31, keep_first=1, diff=0.8)],
+}
+
+
+@pytest.mark.parametrize("name", sorted(TC_STACKS))
+def test_bf16_tensor_core_path_and_plain_path_agree_with_the_oracle(tmp_path, name):
+    """Prompts long enough for several query and key tiles, whole, in portions that straddle tiles, and decoding (the split-key form), on the
+    tensor-core kernels and on the plain kernels (hy_tensor_core = 0)."""
+    cfg = Z.make_config(TC_STACKS[name], width=64, vocab=96)
     W = checkpoint(tmp_path, cfg, seed=13, sharp=2.0)
     toks = tokens_of(cfg, 330, 8)
     want = Z.forward(cfg, W, toks)
