@@ -36,7 +36,7 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
 }
 
-// Every kernel of this file opens with HY_PDL(): it lets the next kernel of the stream become resident early (programmatic dependent
+// Every kernel of the family opens with HY_PDL(): it lets the next kernel of the stream become resident early (programmatic dependent
 // launch) and then waits until every predecessor grid has completed and its memory is visible — nothing is read or written before that, so
 // the kernels stay strictly ordered; what overlaps is only the launch latency and the ramp of the next grid.
 #define HY_PDL() do { griddep_launch(); griddep_wait(); } while (0)

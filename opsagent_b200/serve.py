@@ -3,6 +3,7 @@
 
     python -m opsagent_b200.serve --model llama-3-8b --weights /ckpt/Meta-Llama-3-8B-Instruct --tokenizer /ckpt/.../tokenizer.json \\
         --devices 0,1,2,3 --port 8000 --json-mode
+    python -m opsagent_b200.serve --model-dir /ckpt/zurevik-small --tokenizer /ckpt/.../tokenizer.json      # a hybrid-family checkpoint folder
 
 One engine per device (data-parallel replicas behind one endpoint, BASELINE configs[2]); `--engine '{"kv_gb": 100, ...}'` passes any other engine
 option.  Fails loudly if the CUDA library or a GPU is missing — there is no CPU path."""
@@ -17,6 +18,9 @@ import threading
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m opsagent_b200.serve", description=__doc__.split("\n\n")[0])
     ap.add_argument("--model", default="llama-3-8b", help="preset (llama-3.2-1b, llama-3-8b, qwen2.5-32b, llama-3-70b) or 'custom' with the dimensions in --engine")
+    ap.add_argument("--model-dir", default="", dest="model_dir", help="checkpoint folder (config.json + model.safetensors) of a hybrid-family design; its \"architecture\" "
+                    "(Ratasun, Zurevik) picks the model class, --model is then only the served name")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="float32: hybrid family only")
     ap.add_argument("--weights", default="", help="*.safetensors file or shard directory (empty: seeded random weights)")
     ap.add_argument("--tokenizer", default="", help="tokenizer.json (empty: byte-level ids)")
     ap.add_argument("--devices", default="0", help="comma separated CUDA devices, one replica each")
@@ -32,7 +36,7 @@ def main(argv=None) -> int:
     from .native_front import NativeFront
     from .router import Router
     cfg = {"model": args.model, "weights": args.weights, "tokenizer": args.tokenizer, "model_aliases": "*", "json_mode": int(args.json_mode), "react_tool_steps": args.tool_steps,
-           **json.loads(args.engine)}
+           **({"model_dir": args.model_dir, "dtype": args.dtype, "model": "custom" if args.model == "llama-3-8b" else args.model} if args.model_dir else {}), **json.loads(args.engine)}
     devices = [int(d) for d in args.devices.split(",") if d != ""]
     replicas = Router.create(cfg, devices)                    # engines are created in parallel, one per device
     front = NativeFront(replicas.engines, host=args.host, port=args.port, api_key=args.api_key, tool_steps=args.tool_steps, max_inflight=args.max_inflight)
