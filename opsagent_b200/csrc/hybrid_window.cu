@@ -237,16 +237,19 @@ __global__ void __launch_bounds__(128) hy_win_attention_mma_kernel(HyWinAttn a, 
     const int n_keep = min((min(a.keep_first, lo_min) + WIN_KT - 1) / WIN_KT, win_t0);      // tiles of kept first positions that lie wholly below the window's first tile
     const int n_it = n_keep + (n_kt - win_t0);
     const int32_t* bt = r.block_tables + (long long)seq * r.max_pages_per_seq;
+    // a tile's 32 keys lie in one page (one block-table lookup per tile); a thread walks the tile's 16-byte chunks in steps of 128 with its
+    // (row, chunk) pair advanced by additions
+    const int kc = QD / 8, nc = kc + VD / 8, step_j = 128 / nc, step_c = 128 % nc, j0 = tid / nc, c0 = tid % nc;
     auto load_tile = [&](int it, int buf) {
-        const int kt = it < n_keep ? it : win_t0 + (it - n_keep);
-        const int kc = QD / 8, vc = VD / 8;
-        for (int idx = tid; idx < WIN_KT * (kc + vc); idx += 128) {
-            const int j = idx / (kc + vc), c = idx - j * (kc + vc), key = kt * WIN_KT + j;
+        const int key0 = (it < n_keep ? it : win_t0 + (it - n_keep)) * WIN_KT;
+        const __nv_bfloat16* page = cache + ((long long)bt[key0 >> 6] * 64 + (key0 & 63)) * CW;
+        int j = j0, c = c0;
+        while (j < WIN_KT) {
             __nv_bfloat16* dst = c < kc ? Ks + (buf * WIN_KT + j) * QP + c * 8 : Vs + (buf * WIN_KT + j) * VP + (c - kc) * 8;
-            if (key <= pos_max) {
-                const __nv_bfloat16* row = cache + ((long long)bt[key >> 6] * 64 + (key & 63)) * CW;
-                cp_async16(dst, c < kc ? row + (long long)g * QD + c * 8 : row + KW + (long long)g * VD + (c - kc) * 8);
-            } else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            if (key0 + j <= pos_max) cp_async16(dst, page + (long long)j * CW + (c < kc ? g * QD + c * 8 : KW + g * VD + (c - kc) * 8));
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            j += step_j; c += step_c;
+            if (c >= nc) { c -= nc; ++j; }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -307,13 +310,13 @@ __global__ void __launch_bounds__(128) hy_win_attention_mma_kernel(HyWinAttn a, 
                 // hold no visible key for some of its rows (their window starts later): their maximum then stays -inf
                 const float n_lo = fmaxf(m_lo[mp], mx_lo * qscale), n_hi = fmaxf(m_hi[mp], mx_hi * qscale);
                 const float b_lo = n_lo == -INFINITY ? 0.f : n_lo, b_hi = n_hi == -INFINITY ? 0.f : n_hi;
-                const float c_lo = exp2f(m_lo[mp] - b_lo), c_hi = exp2f(m_hi[mp] - b_hi);
+                const float c_lo = ex2_approx(m_lo[mp] - b_lo), c_hi = ex2_approx(m_hi[mp] - b_hi);
                 m_lo[mp] = n_lo; m_hi[mp] = n_hi;
                 float sum_lo = 0.f, sum_hi = 0.f;
 #pragma unroll
                 for (int nb = 0; nb < 4; ++nb) {
-                    s[nb][0] = exp2f(fmaf(s[nb][0], qscale, -b_lo)); s[nb][1] = exp2f(fmaf(s[nb][1], qscale, -b_lo));
-                    s[nb][2] = exp2f(fmaf(s[nb][2], qscale, -b_hi)); s[nb][3] = exp2f(fmaf(s[nb][3], qscale, -b_hi));
+                    s[nb][0] = ex2_approx(fmaf(s[nb][0], qscale, -b_lo)); s[nb][1] = ex2_approx(fmaf(s[nb][1], qscale, -b_lo));
+                    s[nb][2] = ex2_approx(fmaf(s[nb][2], qscale, -b_hi)); s[nb][3] = ex2_approx(fmaf(s[nb][3], qscale, -b_hi));
                     sum_lo += s[nb][0] + s[nb][1]; sum_hi += s[nb][2] + s[nb][3];
                 }
                 l_lo[mp] = l_lo[mp] * c_lo + sum_lo; l_hi[mp] = l_hi[mp] * c_hi + sum_hi;
@@ -357,7 +360,7 @@ __global__ void __launch_bounds__(128) hy_win_attention_mma_kernel(HyWinAttn a, 
             float up = 1.f;
             if (sink) {                                // the sink joins the denominator (scores are kept in base-2 units)
                 const float s2 = sink[head] * 1.4426950408889634f, M = fmaxf(m, s2);
-                up = m == -INFINITY ? 0.f : exp2f(m - M); l = l * up + exp2f(s2 - M);
+                up = m == -INFINITY ? 0.f : ex2_approx(m - M); l = l * up + ex2_approx(s2 - M);
             }
             f[mp] = l > 0.f ? up / l : 0.f;
         }
@@ -439,18 +442,20 @@ __global__ void __launch_bounds__(256) hy_win_decode_mma_kernel(HyWinAttn a, con
     }
     const float qscale = a.scale * 1.4426950408889634f;
     const int p_lo = qpos[lane >> 2], p_hi = qpos[(lane >> 2) + 8];
+    const int kc = QD / 8, nc = kc + VD / 8, step_j = 32 / nc, step_c = 32 % nc, j0 = lane / nc, c0 = lane % nc;      // a lane walks its warp's tile chunks in steps of 32
     for (int it = warp; it < n_it; it += WIN_DEC_WARPS) {
         const int kt = it < n_keep ? it : win_t0 + (it - n_keep);
         __syncwarp();                                  // the previous tile has been read by every lane
         {
-            const int kc = QD / 8, vc = VD / 8;
-            for (int idx = lane; idx < WIN_KT * (kc + vc); idx += 32) {
-                const int j = idx / (kc + vc), c = idx - j * (kc + vc), key = kt * WIN_KT + j;
+            const int key0 = kt * WIN_KT;              // the tile's 32 keys lie in one page
+            const __nv_bfloat16* page = cache + ((long long)bt[key0 >> 6] * 64 + (key0 & 63)) * CW;
+            int j = j0, c = c0;
+            while (j < WIN_KT) {
                 __nv_bfloat16* dst = c < kc ? Kw + j * QP + c * 8 : Vw + j * VP + (c - kc) * 8;
-                if (key <= pos_max) {
-                    const __nv_bfloat16* row = cache + ((long long)bt[key >> 6] * 64 + (key & 63)) * CW;
-                    cp_async16(dst, c < kc ? row + (long long)g * QD + c * 8 : row + KW + (long long)g * VD + (c - kc) * 8);
-                } else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+                if (key0 + j <= pos_max) cp_async16(dst, page + (long long)j * CW + (c < kc ? g * QD + c * 8 : KW + g * VD + (c - kc) * 8));
+                else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+                j += step_j; c += step_c;
+                if (c >= nc) { c -= nc; ++j; }
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
             asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -486,12 +491,12 @@ __global__ void __launch_bounds__(256) hy_win_decode_mma_kernel(HyWinAttn a, con
             mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)); mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
             const float n_lo = fmaxf(m_lo[mp], mx_lo), n_hi = fmaxf(m_hi[mp], mx_hi);
             const float b_lo = n_lo == -INFINITY ? 0.f : n_lo, b_hi = n_hi == -INFINITY ? 0.f : n_hi;
-            const float c_lo = exp2f(m_lo[mp] - b_lo), c_hi = exp2f(m_hi[mp] - b_hi);
+            const float c_lo = ex2_approx(m_lo[mp] - b_lo), c_hi = ex2_approx(m_hi[mp] - b_hi);
             m_lo[mp] = n_lo; m_hi[mp] = n_hi;
             float sum_lo = 0.f, sum_hi = 0.f;
 #pragma unroll
             for (int nb = 0; nb < 4; ++nb) {
-                s[nb][0] = exp2f(s[nb][0] - b_lo); s[nb][1] = exp2f(s[nb][1] - b_lo); s[nb][2] = exp2f(s[nb][2] - b_hi); s[nb][3] = exp2f(s[nb][3] - b_hi);
+                s[nb][0] = ex2_approx(s[nb][0] - b_lo); s[nb][1] = ex2_approx(s[nb][1] - b_lo); s[nb][2] = ex2_approx(s[nb][2] - b_hi); s[nb][3] = ex2_approx(s[nb][3] - b_hi);
                 sum_lo += s[nb][0] + s[nb][1]; sum_hi += s[nb][2] + s[nb][3];
             }
             l_lo[mp] = l_lo[mp] * c_lo + sum_lo; l_hi[mp] = l_hi[mp] * c_hi + sum_hi;
@@ -543,8 +548,8 @@ __global__ void __launch_bounds__(256) hy_win_decode_mma_kernel(HyWinAttn a, con
 #pragma unroll
         for (int w = 0; w < WIN_DEC_WARPS; ++w) M = fmaxf(M, pm[w][mp][qi]);
 #pragma unroll
-        for (int w = 0; w < WIN_DEC_WARPS; ++w) { wgt[mp][w] = pm[w][mp][qi] == -INFINITY ? 0.f : exp2f(pm[w][mp][qi] - M); L = fmaf(wgt[mp][w], pl[w][mp][qi], L); }
-        if (sink) L += exp2f(sink[head] * 1.4426950408889634f - M);
+        for (int w = 0; w < WIN_DEC_WARPS; ++w) { wgt[mp][w] = pm[w][mp][qi] == -INFINITY ? 0.f : ex2_approx(pm[w][mp][qi] - M); L = fmaf(wgt[mp][w], pl[w][mp][qi], L); }
+        if (sink) L += ex2_approx(sink[head] * 1.4426950408889634f - M);
         inv[mp] = L > 0.f ? 1.0f / L : 0.f;
     }
     float y[NVB / 2], ss = 0.f;
